@@ -1,0 +1,221 @@
+// Row gather (embedding), RMSNorm with and without the residual add, SwiGLU, and the
+// small kernels that turn a step's batch description into per-row indices.
+//
+// Formulas and rounding points: engine/kernels/torch_ref.py:47-58 (RMSNorm: the
+// normalised value is rounded before the gain), :61-68 (residual add rounded once),
+// :74-88 (silu rounded, product rounded).  Reductions are float32 with an order fixed
+// by the block size, so a row's result does not depend on the batch it is in.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void thn_set_error(const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, args);
+    va_end(args);
+}
+
+THN_API const char* thn_last_error() { return g_error; }
+THN_API int thn_abi_version() { return 1; }
+
+// ------------------------------------------------------------------ gather rows
+
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ index,
+                                   int width, int n_table_rows, int* __restrict__ err) {
+    const int m = blockIdx.x;
+    int row = index[m];
+    if (row < 0 || row >= n_table_rows) {
+        if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_TOKEN_RANGE);
+        row = 0;
+    }
+    const T* src = table + (size_t)row * width;
+    T* dst = out + (size_t)m * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+THN_API int thn_gather_rows(void* out, const void* table, const int* index, int n_rows, int width,
+                            int n_table_rows, int dtype, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && width > 0 && n_table_rows > 0, "gather_rows: bad sizes rows=%d width=%d table=%d",
+                  n_rows, width, n_table_rows);
+    if (n_rows == 0) return THN_OK;
+    if (dtype == THN_F32)
+        gather_rows_kernel<float><<<n_rows, 256, 0, stream>>>((float*)out, (const float*)table, index, width,
+                                                              n_table_rows, err);
+    else if (dtype == THN_BF16)
+        gather_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)table, index, width, n_table_rows, err);
+    else
+        THN_CHECK_ARG(false, "gather_rows: unknown dtype %d", dtype);
+    return thn_launch_status("gather_rows");
+}
+
+// ------------------------------------------------------------------ RMSNorm
+
+// y = w * rnd(x * rstd), rstd = 1/sqrt(mean(x^2) + eps).  With ADD: h = rnd(h + d) is
+// stored back first and normalised.  One block per row.
+template <typename T, typename WT, bool ADD>
+__global__ void rmsnorm_kernel(T* __restrict__ y, T* __restrict__ h, const T* __restrict__ d,
+                               const WT* __restrict__ w, int width, float eps) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = to_f32<T>(h[base + i]);
+        if (ADD) {
+            v = rnd<T>(v + to_f32<T>(d[base + i]));
+            h[base + i] = from_f32<T>(v);
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_f32<T>(h[base + i]);
+        y[base + i] = from_f32<T>(to_f32<WT>(w[i]) * rnd<T>(v * rstd));
+    }
+}
+
+template <typename T, typename WT>
+static void launch_rmsnorm(void* y, void* h, const void* d, const void* w, int rows, int width, float eps,
+                           cudaStream_t stream) {
+    const int threads = width >= 2048 ? 512 : 256;
+    if (d)
+        rmsnorm_kernel<T, WT, true><<<rows, threads, 0, stream>>>((T*)y, (T*)h, (const T*)d, (const WT*)w, width, eps);
+    else
+        rmsnorm_kernel<T, WT, false><<<rows, threads, 0, stream>>>((T*)y, (T*)h, nullptr, (const WT*)w, width, eps);
+}
+
+// d == nullptr: y = RMSNorm(h).  Otherwise h is updated in place to rnd(h + d) first.
+THN_API int thn_rmsnorm(void* y, void* h, const void* d, const void* w, int rows, int width, float eps, int dtype,
+                        int w_dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
+    THN_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive, got %g", (double)eps);
+    if (rows == 0) return THN_OK;
+    if (dtype == THN_F32 && w_dtype == THN_F32)
+        launch_rmsnorm<float, float>(y, h, d, w, rows, width, eps, stream);
+    else if (dtype == THN_BF16 && w_dtype == THN_BF16)
+        launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(y, h, d, w, rows, width, eps, stream);
+    else if (dtype == THN_BF16 && w_dtype == THN_F32)
+        launch_rmsnorm<__nv_bfloat16, float>(y, h, d, w, rows, width, eps, stream);
+    else
+        THN_CHECK_ARG(false, "rmsnorm: unsupported dtypes activation=%d gain=%d", dtype, w_dtype);
+    return thn_launch_status("rmsnorm");
+}
+
+// ------------------------------------------------------------------ SwiGLU
+
+// out[m, i] = rnd(rnd(g / (1 + exp(-g))) * u), g = gu[m, i], u = gu[m, inter + i].
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int inter) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const long long m = e / inter;
+        const int i = (int)(e - m * inter);
+        const float g = to_f32<T>(gu[m * 2 * inter + i]);
+        const float u = to_f32<T>(gu[m * 2 * inter + inter + i]);
+        const float s = rnd<T>(g / (1.0f + expf(-g)));
+        out[e] = from_f32<T>(s * u);
+    }
+}
+
+THN_API int thn_swiglu(void* out, const void* gu, int rows, int inter, int dtype, cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    const long long total = (long long)rows * inter;
+    if (total == 0) return THN_OK;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == THN_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gu, total, inter);
+    else if (dtype == THN_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu,
+                                                                     total, inter);
+    else
+        THN_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
+    return thn_launch_status("swiglu");
+}
+
+// ------------------------------------------------------------------ step bookkeeping
+
+// Row m of a packed step belongs to sequence b with cu[b] <= m < cu[b+1]; its slot is
+// slots[b] and its absolute position is seq_lens[slot] + (m - cu[b]).
+__global__ void step_rows_kernel(int* __restrict__ row_slot, int* __restrict__ row_pos,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                 const int* __restrict__ seq_lens, int n_seqs) {
+    const int b = blockIdx.x;
+    if (b >= n_seqs) return;
+    const int r0 = cu_seqlens[b], r1 = cu_seqlens[b + 1];
+    const int slot = slots[b];
+    const int start = seq_lens[slot];
+    for (int r = r0 + threadIdx.x; r < r1; r += blockDim.x) {
+        row_slot[r] = slot;
+        row_pos[r] = start + (r - r0);
+    }
+}
+
+THN_API int thn_step_rows(int* row_slot, int* row_pos, const int* cu_seqlens, const int* slots, const int* seq_lens,
+                          int n_seqs, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0, "step_rows: bad batch %d", n_seqs);
+    if (n_seqs == 0) return THN_OK;
+    step_rows_kernel<<<n_seqs, 128, 0, stream>>>(row_slot, row_pos, cu_seqlens, slots, seq_lens, n_seqs);
+    return thn_launch_status("step_rows");
+}
+
+// seq_lens[slots[b]] += cu[b+1] - cu[b]: the step's tokens are now part of the sequences.
+__global__ void advance_kernel(int* __restrict__ seq_lens, const int* __restrict__ slots,
+                               const int* __restrict__ cu_seqlens, int n_seqs) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < n_seqs) seq_lens[slots[b]] += cu_seqlens[b + 1] - cu_seqlens[b];
+}
+
+THN_API int thn_advance(int* seq_lens, const int* slots, const int* cu_seqlens, int n_seqs, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0, "advance: bad batch %d", n_seqs);
+    if (n_seqs == 0) return THN_OK;
+    advance_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(seq_lens, slots, cu_seqlens, n_seqs);
+    return thn_launch_status("advance");
+}
+
+// ------------------------------------------------------------------ rotary table
+
+// cos/sin of angle = position * inv_freq[i], all float32 (engine/engine.py:238-247).
+__global__ void rope_table_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out,
+                                  const float* __restrict__ inv_freq, int first, int n_positions, int half) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (long long)n_positions * half) return;
+    const int p = (int)(e / half), i = (int)(e - (long long)p * half);
+    const float angle = (float)(first + p) * inv_freq[i];
+    cos_out[(size_t)(first + p) * half + i] = cosf(angle);
+    sin_out[(size_t)(first + p) * half + i] = sinf(angle);
+}
+
+// Fills rows [first, first + n_positions) of tables [*, half].
+THN_API int thn_rope_table(float* cos_out, float* sin_out, const float* inv_freq, int first, int n_positions,
+                           int half, cudaStream_t stream) {
+    THN_CHECK_ARG(first >= 0 && n_positions >= 0 && half > 0, "rope_table: bad sizes");
+    const long long total = (long long)n_positions * half;
+    if (total == 0) return THN_OK;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(cos_out, sin_out, inv_freq, first,
+                                                                           n_positions, half);
+    return thn_launch_status("rope_table");
+}
+
+// ------------------------------------------------------------------ int32 scatter
+
+// dst[index[i]] = value[i]: block-table cells and per-sequence counters changed by the host.
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const long long* __restrict__ index,
+                                   const int* __restrict__ value, int n, long long dst_size) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && index[i] >= 0 && index[i] < dst_size) dst[index[i]] = value[i];
+}
+
+THN_API int thn_scatter_i32(int* dst, const long long* index, const int* value, int n, long long dst_size,
+                            cudaStream_t stream) {
+    THN_CHECK_ARG(n >= 0 && dst_size >= 0, "scatter_i32: bad sizes");
+    if (n == 0) return THN_OK;
+    scatter_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, index, value, n, dst_size);
+    return thn_launch_status("scatter_i32");
+}

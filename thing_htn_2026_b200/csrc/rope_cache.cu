@@ -1,0 +1,116 @@
+// Fused per-head RMSNorm of q and k, rotary position encoding, and the write of K and V
+// into the paged cache.  One warp per (row, head).
+//
+// Formulas: engine/kernels/torch_ref.py:141-162 (column layout Nq q heads, Nkv k heads,
+// Nkv v heads; norm before rotation; V copied untouched) and :94-104 (rotation:
+// out = rnd(rnd(x*cos) + rnd(rotate_half(x)*sin)), rotate_half(x) = cat(-x[D/2:], x[:D/2])).
+// The angle tables are float32 (engine/engine.py:238-247); with bfloat16 activations
+// cos and sin are rounded to bfloat16 as the reference's tables are (:246-247).
+#include "common.cuh"
+
+constexpr int kMaxHeadDim = 512;
+
+template <typename T, typename WT>
+__global__ void qk_norm_rope_cache_kernel(
+    T* __restrict__ q_out, const T* __restrict__ qkv, const WT* __restrict__ q_gain, const WT* __restrict__ k_gain,
+    float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int table_len, int rotary_dim,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_rows, int n_q, int write_cache,
+    int* __restrict__ err) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
+    const int n_heads_total = n_q + 2 * kv.n_kv;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + warp_in_block;
+    if (unit >= (long long)n_rows * n_heads_total) return;
+    const int m = (int)(unit / n_heads_total), head = (int)(unit - (long long)m * n_heads_total);
+    const int D = kv.head_dim;
+    const bool is_q = head < n_q, is_k = !is_q && head < n_q + kv.n_kv;
+    if (!is_q && !write_cache) return;
+    float* buf = smem + warp_in_block * D;
+    const T* src = qkv + (size_t)m * n_heads_total * D + (size_t)head * D;
+    const int pos = row_pos[m];
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)m * n_q * D + (size_t)head * D;
+    } else {
+        const int kvh = is_k ? head - n_q : head - n_q - kv.n_kv;
+        const int page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
+        if (page < 0) {
+            if (lane == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            return;
+        }
+        dst = (T*)kv.base + kv_offset(kv, page, is_k ? 0 : 1, kvh, pos % kv.page_size);
+    }
+
+    if (!is_q && !is_k) {  // V: plain copy
+        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        return;
+    }
+
+    const WT* gain = is_q ? q_gain : k_gain;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+        const float v = to_f32<T>(src[d]);
+        buf[d] = v;
+        ss += v * v;
+    }
+    if (gain) {
+        ss = warp_sum(ss);
+        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int d = lane; d < D; d += 32) buf[d] = rnd<T>(to_f32<WT>(gain[d]) * rnd<T>(buf[d] * rstd));
+    }
+    __syncwarp();
+    if (cos_tab == nullptr) {
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(buf[d]);
+        return;
+    }
+    if (pos >= table_len) {
+        if (lane == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+        return;
+    }
+    const int half = rotary_dim / 2;
+    const float* c_row = cos_tab + (size_t)pos * half;
+    const float* s_row = sin_tab + (size_t)pos * half;
+    for (int d = lane; d < D; d += 32) {
+        float out = buf[d];
+        if (d < rotary_dim) {
+            const int i = d < half ? d : d - half;
+            const float c = rnd<T>(c_row[i]), s = rnd<T>(s_row[i]);
+            const float rotated = d < half ? -buf[d + half] : buf[d - half];
+            out = rnd<T>(rnd<T>(out * c) + rnd<T>(rotated * s));
+        }
+        dst[d] = from_f32<T>(out);
+    }
+}
+
+// qkv [n_rows, (n_q + 2*n_kv) * head_dim] -> q_out [n_rows, n_q * head_dim]; K and V of
+// every row go to (slot, position) of the cache entry unless write_cache == 0.
+// q_gain/k_gain may be null (no head norm); cos_tab may be null (no rotation).
+THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const void* q_gain, const void* k_gain, int w_dtype,
+                                   float eps, const float* cos_tab, const float* sin_tab, int table_len,
+                                   int rotary_dim, const int* row_slot, const int* row_pos, void* kv_base,
+                                   const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
+                                   int n_rows, int n_q, int write_cache, int dtype, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_rows >= 0 && n_q > 0 && n_kv > 0 && page_size > 0, "qk_norm_rope_cache: bad sizes");
+    THN_UNSUPPORTED_IF(head_dim <= 0 || head_dim > kMaxHeadDim, "qk_norm_rope_cache: head_dim %d not in [1, %d]",
+                       head_dim, kMaxHeadDim);
+    THN_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
+                  "qk_norm_rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
+    THN_CHECK_ARG((q_gain == nullptr) == (k_gain == nullptr), "qk_norm_rope_cache: q and k gains come together");
+    if (n_rows == 0) return THN_OK;
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
+    const int warps = 4;
+    const long long units = (long long)n_rows * (n_q + 2 * n_kv);
+    const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+    const size_t smem = (size_t)warps * head_dim * sizeof(float);
+#define LAUNCH(T, WT)                                                                                              \
+    qk_norm_rope_cache_kernel<T, WT><<<blocks, warps * 32, smem, stream>>>(                                        \
+        (T*)q_out, (const T*)qkv, (const WT*)q_gain, (const WT*)k_gain, eps, cos_tab, sin_tab, table_len,          \
+        rotary_dim, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)
+    if (dtype == THN_F32 && w_dtype == THN_F32) LAUNCH(float, float);
+    else if (dtype == THN_BF16 && w_dtype == THN_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == THN_BF16 && w_dtype == THN_F32) LAUNCH(__nv_bfloat16, float);
+    else THN_CHECK_ARG(false, "qk_norm_rope_cache: unsupported dtypes activation=%d gain=%d", dtype, w_dtype);
+#undef LAUNCH
+    return thn_launch_status("qk_norm_rope_cache");
+}

@@ -1,0 +1,106 @@
+// Token choice from float32 logits: greedy argmax and temperature sampling.
+//
+// Greedy: the lowest index among exact ties (engine/engine.py:1121;
+// OPTIMIZATION_GUIDE.md:213).  The reference samples with nothing else.  Temperature
+// sampling uses the Gumbel-max rule: argmax(logit / T + noise) is a draw from
+// softmax(logit / T).  The noise of vocabulary entry i is word i % 4 of
+// Philox-4x32-10(counter = (i / 4, step, stream, 0), key = seed), u = ((word >> 9) + 0.5)
+// * 2^-23, noise = -log(-log(u)); a sequence's draws depend on its own (seed, stream,
+// step) only, never on its batch mates.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+struct Best {
+    float value;
+    int index;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+    if (b.value > a.value || (b.value == a.value && b.index < a.index)) return b;
+    return a;
+}
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                              uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// One block per row.  temperature == nullptr or temperature[row] == 0: greedy.
+__global__ void __launch_bounds__(1024) choose_kernel(int* __restrict__ out, const float* __restrict__ logits,
+                                                      int vocab, long long row_stride,
+                                                      const float* __restrict__ temperature,
+                                                      const unsigned long long* __restrict__ seed,
+                                                      const int* __restrict__ stream_id,
+                                                      const int* __restrict__ step) {
+    __shared__ Best partial[32];
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * row_stride;
+    const float temp = temperature ? temperature[row] : 0.f;
+    Best best{-INFINITY, 0x7fffffff};
+    if (temp == 0.f) {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = better(best, Best{x[i], i});
+    } else {
+        const unsigned long long s = seed[row];
+        const uint32_t k0 = (uint32_t)s, k1 = (uint32_t)(s >> 32);
+        const uint32_t c1 = (uint32_t)step[row], c2 = (uint32_t)stream_id[row];
+        const int n_blocks = (vocab + 3) / 4;
+        for (int b = threadIdx.x; b < n_blocks; b += blockDim.x) {
+            uint32_t words[4];
+            philox4x32_10((uint32_t)b, c1, c2, 0u, k0, k1, words);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = 4 * b + j;
+                if (i < vocab) {
+                    const float u = ((float)(words[j] >> 9) + 0.5f) * 1.1920928955078125e-07f;  // 2^-23
+                    const float noise = -logf(-logf(u));
+                    best = better(best, Best{x[i] / temp + noise, i});
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+        best = better(best, other);
+    }
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int n_warps = (blockDim.x + 31) >> 5;
+        best = threadIdx.x < n_warps ? partial[threadIdx.x] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+            best = better(best, other);
+        }
+        if (threadIdx.x == 0) out[row] = best.index == 0x7fffffff ? 0 : best.index;
+    }
+}
+}  // namespace
+
+// logits [rows, vocab] float32 with row stride row_stride elements -> out [rows] int32.
+// temperature, seed, stream_id, step are per-row device arrays; temperature may be null
+// (all greedy), in which case the others are not read.
+THN_API int thn_choose_tokens(int* out, const float* logits, int rows, int vocab, long long row_stride,
+                              const float* temperature, const unsigned long long* seed, const int* stream_id,
+                              const int* step, cudaStream_t stream) {
+    THN_CHECK_ARG(rows >= 0 && vocab > 0 && row_stride >= vocab, "choose_tokens: bad sizes rows=%d vocab=%d", rows,
+                  vocab);
+    THN_CHECK_ARG(temperature == nullptr || (seed && stream_id && step),
+                  "choose_tokens: sampling needs seed, stream and step arrays");
+    if (rows == 0) return THN_OK;
+    const int threads = vocab >= 4096 ? 1024 : 256;
+    choose_kernel<<<rows, threads, 0, stream>>>(out, logits, vocab, row_stride, temperature, seed, stream_id, step);
+    return thn_launch_status("choose_tokens");
+}

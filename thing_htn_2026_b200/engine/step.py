@@ -1,0 +1,81 @@
+"""The step function: one batch of sequences, the tokens it brings, logits where wanted.
+
+A step runs only the tokens it is given, as one packed batch ``[sum of lengths]`` with no
+padding, on top of what earlier steps left in the cache.  The sequences of a step either
+all start (prompts of unequal lengths, one step) or all go on by one token; the kernels
+make no such distinction: every row carries its slot and its absolute position.
+
+The reference has two functions with equal lengths only: ``_prefill_slice`` for prompts
+(engine/engine.py:1191-1221) and ``_step`` for T tokens per sequence
+(engine/engine.py:1093-1121); both return token ids, never logits.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.sequence_cache import SequenceCache
+from ..parts import StepContext
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()     # places among ``tokens`` whose logits are asked for
+
+
+class StepRunner:
+    """Owns the device error word and drives ``model`` over ``cache``."""
+
+    def __init__(self, model, cache: SequenceCache):
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.err = ops.new_error_word(self.device)
+        model.ensure_positions(cache.max_pages_per_seq * cache.page_size)
+
+    def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
+        """Runs the entries' tokens; returns float32 logits ``[wanted, vocab]`` in the order
+        of the entries and of their ``want``.  Raises CacheFull before touching anything if
+        the cache cannot take the tokens."""
+        entries = [e for e in entries]
+        slots = [e.slot for e in entries]
+        counts = [len(e.tokens) for e in entries]
+        if any(c == 0 for c in counts):
+            raise ValueError("a step entry brings no tokens")
+        n_rows = sum(counts)
+        cu = [0]
+        for c in counts:
+            cu.append(cu[-1] + c)
+        want_rows: List[int] = []
+        for e, start in zip(entries, cu):
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")
+                want_rows.append(start + w)
+        self.cache.prepare(slots, counts)
+
+        flat = [t for e in entries for t in e.tokens] + cu + slots + want_rows
+        packed = torch.tensor(flat, dtype=torch.int32).to(self.device)
+        tokens = packed[:n_rows]
+        cu_dev = packed[n_rows:n_rows + len(cu)]
+        slots_dev = packed[n_rows + len(cu):n_rows + len(cu) + len(slots)]
+        want_dev = packed[n_rows + len(cu) + len(slots):]
+
+        rows = ops.step_rows(cu_dev, slots_dev, self.cache.seq_lens, n_rows, max(counts))
+        ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
+        h, d = self.model.hidden(tokens, ctx)
+        if want_rows:
+            logits = self.model.logits(h, d, want_dev)
+        else:
+            logits = torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        ops.advance(self.cache.seq_lens, slots_dev, cu_dev)
+        self.cache.commit(slots, counts)
+        if check:
+            ops.raise_on_device_error(self.err, "step")
+        return logits

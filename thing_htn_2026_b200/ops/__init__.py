@@ -1,0 +1,326 @@
+"""Python faces of the CUDA kernels.  Every function here takes CUDA tensors and launches
+on the current stream; there is no CPU path.  Matrix products of the bfloat16 path may
+go to the vendor library, as the reference's do (engine/engine.py:341-350); everything
+else, and every product of the 32-bit path, is this library's own kernel.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import library
+from .library import KernelLibraryError
+
+c_int, c_float, c_void_p, c_longlong = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+# device error word bits (csrc/common.cuh)
+ERR_TOKEN_RANGE, ERR_PAGE_UNMAPPED, ERR_POSITION_RANGE, ERR_WAIT_TIMEOUT = 1, 2, 4, 8
+_ERR_TEXT = {
+    ERR_TOKEN_RANGE: "a token id outside the vocabulary",
+    ERR_PAGE_UNMAPPED: "a cache position whose page is not mapped",
+    ERR_POSITION_RANGE: "a position beyond the rotary table",
+    ERR_WAIT_TIMEOUT: "a bounded wait inside a kernel gave up",
+}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments, or a kernel reported a fault."""
+
+
+_SIGNATURES = {
+    "thn_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "thn_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_step_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "thn_advance": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "thn_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+    "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_scatter_i32": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p],
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        loaded = library.load()
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(loaded, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = loaded
+    return _lib
+
+
+def _call(name: str, *args) -> None:
+    code = getattr(lib(), name)(*args)
+    if code:
+        raise KernelError(f"{name}: {lib().thn_last_error().decode()} (status {code})")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, what: str, dtype=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; this library runs on CUDA only")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    return t
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def new_error_word(device) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def raise_on_device_error(err: torch.Tensor, where: str) -> None:
+    """Reads the error word (a synchronising copy) and raises if a kernel set a bit."""
+    bits = int(err.item())
+    if bits:
+        err.zero_()
+        reasons = [text for bit, text in _ERR_TEXT.items() if bits & bit]
+        raise KernelError(f"{where}: device reported " + "; ".join(reasons))
+
+
+# ------------------------------------------------------------------ rows and lengths
+
+
+@dataclass
+class StepRows:
+    """Per-row indices of a packed step: the slot of each row's sequence and the row's
+    absolute position; plus the batch description they were made from."""
+
+    row_slot: torch.Tensor   # int32 [rows]
+    row_pos: torch.Tensor    # int32 [rows]
+    slots: torch.Tensor      # int32 [seqs]
+    cu_seqlens: torch.Tensor  # int32 [seqs + 1]
+    n_rows: int
+    n_seqs: int
+    max_q_len: int           # longest run of rows of one sequence (host knowledge)
+
+
+def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Tensor, n_rows: int,
+              max_q_len: int, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> StepRows:
+    _need(cu_seqlens, "step_rows cu_seqlens", torch.int32)
+    _need(slots, "step_rows slots", torch.int32)
+    _need(seq_lens, "step_rows seq_lens", torch.int32)
+    n_seqs = slots.shape[0]
+    if out is None:
+        row_slot = torch.empty(n_rows, dtype=torch.int32, device=slots.device)
+        row_pos = torch.empty(n_rows, dtype=torch.int32, device=slots.device)
+    else:
+        row_slot, row_pos = out
+    _call("thn_step_rows", _ptr(row_slot), _ptr(row_pos), _ptr(cu_seqlens), _ptr(slots), _ptr(seq_lens), n_seqs,
+          _stream())
+    return StepRows(row_slot, row_pos, slots, cu_seqlens, n_rows, n_seqs, max_q_len)
+
+
+def advance(seq_lens: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor) -> None:
+    _call("thn_advance", _ptr(_need(seq_lens, "advance seq_lens", torch.int32)), _ptr(slots), _ptr(cu_seqlens),
+          slots.shape[0], _stream())
+
+
+def scatter_i32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor) -> None:
+    """dst.view(-1)[index[i]] = value[i]; index int64, value int32, all on the device."""
+    _need(dst, "scatter_i32 dst", torch.int32)
+    _need(index, "scatter_i32 index", torch.int64)
+    _need(value, "scatter_i32 value", torch.int32)
+    _call("thn_scatter_i32", _ptr(dst), _ptr(index), _ptr(value), index.shape[0], dst.numel(), _stream())
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+def gather_rows(table: torch.Tensor, index: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m] = table[index[m]]; an index outside the table sets ERR_TOKEN_RANGE."""
+    _need(table, "gather_rows table")
+    _need(index, "gather_rows index", torch.int32)
+    out = torch.empty((index.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+    _call("thn_gather_rows", _ptr(out), _ptr(table), _ptr(index), index.shape[0], table.shape[1], table.shape[0],
+          _code(table, "gather_rows"), _ptr(err), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    _need(x, "rmsnorm x")
+    _need(gain, "rmsnorm gain")
+    if gain.shape[0] != x.shape[-1]:
+        raise KernelError(f"rmsnorm: gain has {gain.shape[0]} entries, rows have {x.shape[-1]}")
+    y = torch.empty_like(x)
+    rows = x.numel() // x.shape[-1]
+    _call("thn_rmsnorm", _ptr(y), _ptr(x), None, _ptr(gain), rows, x.shape[-1], float(eps), _code(x, "rmsnorm"),
+          _code(gain, "rmsnorm gain"), _stream())
+    return y
+
+
+def add_rmsnorm(h: torch.Tensor, d: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """h <- round(h + d) in place; returns RMSNorm(h) * gain."""
+    _need(h, "add_rmsnorm h")
+    _need(d, "add_rmsnorm d", h.dtype)
+    _need(gain, "add_rmsnorm gain")
+    if d.shape != h.shape or gain.shape[0] != h.shape[-1]:
+        raise KernelError(f"add_rmsnorm: shapes h {tuple(h.shape)}, d {tuple(d.shape)}, gain {tuple(gain.shape)}")
+    y = torch.empty_like(h)
+    rows = h.numel() // h.shape[-1]
+    _call("thn_rmsnorm", _ptr(y), _ptr(h), _ptr(d), _ptr(gain), rows, h.shape[-1], float(eps),
+          _code(h, "add_rmsnorm"), _code(gain, "add_rmsnorm gain"), _stream())
+    return y
+
+
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """gu [rows, 2*I] (gate columns first) -> silu(gate) * up, [rows, I]."""
+    _need(gu, "swiglu")
+    rows, width = gu.shape
+    if width % 2:
+        raise KernelError(f"swiglu: width {width} is odd")
+    out = torch.empty((rows, width // 2), dtype=gu.dtype, device=gu.device)
+    _call("thn_swiglu", _ptr(out), _ptr(gu), rows, width // 2, _code(gu, "swiglu"), _stream())
+    return out
+
+
+def rope_table(cos: torch.Tensor, sin: torch.Tensor, inv_freq: torch.Tensor, first: int, count: int) -> None:
+    _need(cos, "rope_table cos", torch.float32)
+    _need(sin, "rope_table sin", torch.float32)
+    _need(inv_freq, "rope_table inv_freq", torch.float32)
+    if first + count > cos.shape[0]:
+        raise KernelError(f"rope_table: rows [{first}, {first + count}) exceed the table of {cos.shape[0]}")
+    _call("thn_rope_table", _ptr(cos), _ptr(sin), _ptr(inv_freq), first, count, inv_freq.shape[0], _stream())
+
+
+# ------------------------------------------------------------------ matrix products
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16: the
+    vendor library's tensor-core product with float32 accumulation (the reference's
+    choice, engine/engine.py:341-350); ``out_dtype=torch.float32`` keeps the
+    accumulator's precision (used for logits)."""
+    _need(x, "linear x")
+    _need(weight, "linear weight", x.dtype)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
+        raise KernelError(f"linear: shapes x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    if x.dtype == torch.float32:
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        _call("thn_gemm_f32", _ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0], x.shape[1], _stream())
+        return out
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: dtype {x.dtype} is not supported")
+    if out_dtype in (None, torch.bfloat16):
+        return torch.nn.functional.linear(x, weight)
+    return torch.mm(x, weight.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------ attention
+
+
+@dataclass
+class KVView:
+    """One cache entry as the kernels see it."""
+
+    storage: torch.Tensor       # [pages, 2, n_kv, page_size, head_dim] of this entry
+    block_table: torch.Tensor   # int32 [max_slots, max_pages_per_seq]
+    n_kv: int
+    page_size: int
+    head_dim: int
+
+
+@dataclass
+class RotaryTables:
+    cos: torch.Tensor   # float32 [positions, rotary_dim / 2]
+    sin: torch.Tensor
+    rotary_dim: int
+
+
+def qk_norm_rope_cache(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+                       eps: float, rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int,
+                       write_cache: bool, err: torch.Tensor) -> torch.Tensor:
+    _need(qkv, "qk_norm_rope_cache qkv")
+    width = (n_q + 2 * kv.n_kv) * kv.head_dim
+    if qkv.shape != (rows.n_rows, width):
+        raise KernelError(f"qk_norm_rope_cache: qkv is {tuple(qkv.shape)}, expected {(rows.n_rows, width)}")
+    if kv.storage.dtype != qkv.dtype:
+        raise KernelError(f"qk_norm_rope_cache: cache is {kv.storage.dtype}, activations {qkv.dtype}")
+    q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=qkv.dtype, device=qkv.device)
+    w_code = _code(q_gain, "qk gains") if q_gain is not None else _code(qkv, "qkv")
+    _call("thn_qk_norm_rope_cache", _ptr(q), _ptr(qkv), _ptr(q_gain), _ptr(k_gain), w_code, float(eps),
+          _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
+          rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
+          _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
+          kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, rows.n_rows, n_q, int(write_cache),
+          _code(qkv, "qkv"), _ptr(err), _stream())
+    return q
+
+
+def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+                      window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+    _need(q, "attention q")
+    out = torch.empty_like(q)
+    _call("thn_attention_generic", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage),
+          _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, rows.n_rows, n_q,
+          float(scale), int(window or 0), _code(q, "attention"), _ptr(err), _stream())
+    return out
+
+
+def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
+              err: torch.Tensor) -> torch.Tensor:
+    """Causal attention of the step's rows over the cache (which already holds the step's
+    own keys).  Chooses the kernel by dtype, head size and step shape."""
+    return attention_generic(q, rows, kv, n_q, scale, window, err)
+
+
+# ------------------------------------------------------------------ token choice
+
+
+def choose_tokens(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+                  seed: Optional[torch.Tensor] = None, stream_id: Optional[torch.Tensor] = None,
+                  step: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """logits float32 [rows, vocab] -> int32 [rows].  Rows with temperature 0 (or no
+    temperature tensor at all) take the argmax, lowest index on ties; others are drawn
+    from softmax(logits / T) with Philox noise keyed by (seed, stream, step) of the row."""
+    _need(logits, "choose_tokens logits", torch.float32)
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32)
+        _need(seed, "seed", torch.int64)
+        _need(stream_id, "stream", torch.int32)
+        _need(step, "step", torch.int32)
+    _call("thn_choose_tokens", _ptr(out), _ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature),
+          _ptr(seed), _ptr(stream_id), _ptr(step), _stream())
+    return out
+
+
+__all__ = [
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "add_rmsnorm", "advance",
+    "attention", "attention_generic", "choose_tokens", "gather_rows", "lib", "linear", "new_error_word",
+    "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+]

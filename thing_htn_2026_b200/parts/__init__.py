@@ -1,0 +1,5 @@
+from . import attention, block, embedding, feedforward, norms, positions  # noqa: F401  (registration)
+from .registry import FAMILIES, part_class, register_part, unregister_part
+from .runtime import Runtime, StepContext
+
+__all__ = ["FAMILIES", "part_class", "register_part", "unregister_part", "Runtime", "StepContext"]

@@ -1,0 +1,44 @@
+"""Token embedding (a row gather, engine/engine.py:1101) and the LM head
+(engine/engine.py:1120; with tied weights it is the embedding table, :225-226).
+Logits are float32."""
+
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import ops
+from ..config.base import PartSpec
+from ..weights.loader import MATRIX, TensorSpec
+from .registry import register_part
+from .runtime import Runtime
+
+
+@register_part("embedding", "embedding")
+class Embedding:
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        return [TensorSpec(spec.tensors["weight"], (int(spec.params["vocab_size"]), int(spec.params["hidden_size"])),
+                           MATRIX)]
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        self.table = runtime.tensor(spec, "weight")
+
+    def forward(self, tokens: torch.Tensor, err: torch.Tensor) -> torch.Tensor:
+        return ops.gather_rows(self.table, tokens, err)
+
+
+@register_part("head", "lm_head")
+class LMHead:
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        return [TensorSpec(spec.tensors["weight"], (int(spec.params["vocab_size"]), int(spec.params["hidden_size"])),
+                           MATRIX)]
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        self.weight = runtime.tensor(spec, "weight")
+        self.vocab_size = int(spec.params["vocab_size"])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, out_dtype=torch.float32)
