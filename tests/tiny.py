@@ -58,3 +58,8 @@ def write_model(folder, name, gain_std=0.1):
 def tokens(name, length, seed):
     g = torch.Generator().manual_seed(1000 + seed)
     return torch.randint(0, CONFIGS[name]["vocab_size"], (length,), generator=g).tolist()
+
+
+def tokens_for_dir(model_dir, length):
+    """Tokens for the configuration whose folder this is (folders are named by configuration)."""
+    return tokens(os.path.basename(os.path.normpath(model_dir)), length, 999)

@@ -2,3 +2,10 @@
 cache, step function, generation loop, sampling and the CUDA kernels under them."""
 
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    if name == "Engine":
+        from .engine.engine import Engine
+        return Engine
+    raise AttributeError(name)

@@ -219,3 +219,17 @@ THN_API int thn_scatter_i32(int* dst, const long long* index, const int* value, 
     scatter_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, index, value, n, dst_size);
     return thn_launch_status("scatter_i32");
 }
+
+// out[i] = src[index[i]]: the tokens that the sequences of a decode step feed next.
+__global__ void gather_i32_kernel(int* __restrict__ out, const int* __restrict__ src, const int* __restrict__ index,
+                                  int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = src[index[i]];
+}
+
+THN_API int thn_gather_i32(int* out, const int* src, const int* index, int n, cudaStream_t stream) {
+    THN_CHECK_ARG(n >= 0, "gather_i32: bad size %d", n);
+    if (n == 0) return THN_OK;
+    gather_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(out, src, index, n);
+    return thn_launch_status("gather_i32");
+}

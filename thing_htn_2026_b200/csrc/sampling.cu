@@ -41,19 +41,21 @@ __global__ void __launch_bounds__(1024) choose_kernel(int* __restrict__ out, con
                                                       int vocab, long long row_stride,
                                                       const float* __restrict__ temperature,
                                                       const unsigned long long* __restrict__ seed,
-                                                      const int* __restrict__ stream_id,
-                                                      const int* __restrict__ step) {
+                                                      const int* __restrict__ stream_id, int* __restrict__ step,
+                                                      const int* __restrict__ slots, int* __restrict__ last_token,
+                                                      int bump_step) {
     __shared__ Best partial[32];
     const int row = blockIdx.x;
+    const int who = slots ? slots[row] : row;  // index of this row's per-sequence values
     const float* x = logits + (size_t)row * row_stride;
-    const float temp = temperature ? temperature[row] : 0.f;
+    const float temp = temperature ? temperature[who] : 0.f;
     Best best{-INFINITY, 0x7fffffff};
     if (temp == 0.f) {
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) best = better(best, Best{x[i], i});
     } else {
-        const unsigned long long s = seed[row];
+        const unsigned long long s = seed[who];
         const uint32_t k0 = (uint32_t)s, k1 = (uint32_t)(s >> 32);
-        const uint32_t c1 = (uint32_t)step[row], c2 = (uint32_t)stream_id[row];
+        const uint32_t c1 = (uint32_t)step[who], c2 = (uint32_t)stream_id[who];
         const int n_blocks = (vocab + 3) / 4;
         for (int b = threadIdx.x; b < n_blocks; b += blockDim.x) {
             uint32_t words[4];
@@ -84,23 +86,32 @@ __global__ void __launch_bounds__(1024) choose_kernel(int* __restrict__ out, con
             Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
             best = better(best, other);
         }
-        if (threadIdx.x == 0) out[row] = best.index == 0x7fffffff ? 0 : best.index;
+        if (threadIdx.x == 0) {
+            const int token = best.index == 0x7fffffff ? 0 : best.index;
+            out[row] = token;
+            if (last_token) last_token[who] = token;
+            if (bump_step && step) step[who] += 1;
+        }
     }
 }
 }  // namespace
 
 // logits [rows, vocab] float32 with row stride row_stride elements -> out [rows] int32.
-// temperature, seed, stream_id, step are per-row device arrays; temperature may be null
-// (all greedy), in which case the others are not read.
+// temperature, seed, stream_id, step are device arrays indexed by row, or by slots[row]
+// when slots is given (per-sequence state); temperature may be null (all greedy), in which
+// case seed and stream_id are not read.  With last_token the choice is also stored at the
+// same index (the token the sequence feeds next); with bump_step the step counter at that
+// index grows by one after it was used.
 THN_API int thn_choose_tokens(int* out, const float* logits, int rows, int vocab, long long row_stride,
                               const float* temperature, const unsigned long long* seed, const int* stream_id,
-                              const int* step, cudaStream_t stream) {
+                              int* step, const int* slots, int* last_token, int bump_step, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && vocab > 0 && row_stride >= vocab, "choose_tokens: bad sizes rows=%d vocab=%d", rows,
                   vocab);
     THN_CHECK_ARG(temperature == nullptr || (seed && stream_id && step),
                   "choose_tokens: sampling needs seed, stream and step arrays");
     if (rows == 0) return THN_OK;
     const int threads = vocab >= 4096 ? 1024 : 256;
-    choose_kernel<<<rows, threads, 0, stream>>>(out, logits, vocab, row_stride, temperature, seed, stream_id, step);
+    choose_kernel<<<rows, threads, 0, stream>>>(out, logits, vocab, row_stride, temperature, seed, stream_id, step,
+                                                slots, last_token, bump_step);
     return thn_launch_status("choose_tokens");
 }

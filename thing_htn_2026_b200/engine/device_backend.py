@@ -1,0 +1,188 @@
+"""Device side of the generation loop: prefill through the step function, single-token
+steps as one CUDA graph per batch size, token choice on the device, tokens back to the
+host through a ring of pinned buffers.
+
+Per-sequence state of fixed size, indexed by slot (beside ``seq_lens``): the token the
+sequence feeds next, its sampling step counter, temperature, seed and stream.  A decode
+step reads its batch as a list of slots from a static buffer, so one captured graph
+serves every batch of that size; the next token never visits the host before it is fed
+back.  (The reference keeps a token history and positions on the device for the same
+reason, engine/engine.py:941-953, and captures the step once per shape, :1005-1042.)
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..cache.sequence_cache import SequenceCache
+from ..parts import StepContext
+from .generation import Request, tokens_needed
+from .step import StepEntry, StepRunner
+
+
+@dataclass
+class _Handle:
+    buffer: torch.Tensor     # pinned int32
+    event: torch.cuda.Event
+    count: int
+
+
+class DeviceBackend:
+    def __init__(self, model, cache: SequenceCache, *, max_batch: int = 64, use_graphs: bool = True,
+                 ring: int = 8):
+        self.model, self.cache = model, cache
+        self.device = model.device
+        self.page_size = cache.page_size
+        self._max_batch = min(int(max_batch), cache.max_slots - 1)
+        self.use_graphs = bool(use_graphs)
+        self.runner = StepRunner(model, cache)
+        self.err = self.runner.err
+        state = cache.sequence_state
+        self.last_token = state("last_token", (), torch.int32)
+        self.sample_step = state("sample_step", (), torch.int32)
+        self.temperature = state("temperature", (), torch.float32)
+        self.seed = state("seed", (), torch.int64)
+        self.stream_id = state("stream", (), torch.int32)
+
+        n = self._max_batch
+        dev = self.device
+        self.slots_buf = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.cu_buf = torch.arange(n + 1, dtype=torch.int32, device=dev)
+        self.tokens_in = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.out_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.row_slot = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.row_pos = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._composition: Optional[Tuple[int, ...]] = None
+        self._ring = [(torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                      for _ in range(ring)]
+        self._stage = [torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True) for _ in range(ring)]
+        self._ring_next = 0
+        self._sampling = False
+        # One slot with one page stays reserved: decode graphs are warmed up on it.
+        (self._scratch_slot,) = cache.open(1)
+        cache.prepare([self._scratch_slot], [1])
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ capacity
+
+    def capacity_tokens(self) -> int:
+        return (self.cache.n_pages - 1) * self.page_size
+
+    def max_batch(self) -> int:
+        return self._max_batch
+
+    # ------------------------------------------------------------------ batches
+
+    def open_batch(self, requests: Sequence[Request]) -> List[int]:
+        slots = self.cache.open(len(requests))
+        try:
+            self.cache.prepare(slots, [tokens_needed(r, 1) for r in requests])
+        except Exception:
+            self.cache.close(slots)
+            raise
+        index = torch.tensor(slots, dtype=torch.int64, device=self.device)
+        self.temperature.index_copy_(0, index, torch.tensor([r.temperature for r in requests], dtype=torch.float32,
+                                                            device=self.device))
+        self.seed.index_copy_(0, index, torch.tensor([_as_i64(r.seed) for r in requests], dtype=torch.int64,
+                                                     device=self.device))
+        self.stream_id.index_copy_(0, index, torch.tensor([r.stream & 0x7FFFFFFF for r in requests],
+                                                          dtype=torch.int32, device=self.device))
+        self._sampling = any(r.temperature > 0 for r in requests)
+        self._composition = None
+        return slots
+
+    def close_batch(self, slots: Sequence[int]) -> None:
+        self.cache.close(slots)
+        ops.raise_on_device_error(self.err, "generation")
+
+    # ------------------------------------------------------------------ steps
+
+    def _choose(self, logits: torch.Tensor, slots_dev: torch.Tensor, out: torch.Tensor) -> None:
+        ops.choose_tokens(logits, self.temperature, self.seed, self.stream_id, self.sample_step, out=out,
+                          slots=slots_dev, last_token=self.last_token, bump_step=True)
+
+    def _send(self, tokens_dev: torch.Tensor, count: int) -> _Handle:
+        buffer, event = self._ring[self._ring_next]
+        self._ring_next = (self._ring_next + 1) % len(self._ring)
+        buffer[:count].copy_(tokens_dev[:count], non_blocking=True)
+        event.record()
+        return _Handle(buffer, event, count)
+
+    def launch_prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> _Handle:
+        entries = [StepEntry(slot, prompt, (len(prompt) - 1,)) for slot, prompt in zip(slots, prompts)]
+        logits = self.runner.step(entries, check=False)
+        slots_dev = torch.tensor(list(slots), dtype=torch.int32).to(self.device)
+        out = torch.empty(len(slots), dtype=torch.int32, device=self.device)
+        self._choose(logits, slots_dev, out)
+        return self._send(out, len(slots))
+
+    def _decode_program(self, batch: int) -> None:
+        """One token for each of the first ``batch`` slots of ``slots_buf``; everything it
+        reads and writes is per-sequence state or a static buffer."""
+        slots = self.slots_buf[:batch]
+        cu = self.cu_buf[:batch + 1]
+        tokens = ops.gather_i32(self.last_token, slots, out=self.tokens_in[:batch])
+        rows = ops.step_rows(cu, slots, self.cache.seq_lens, batch, 1,
+                             out=(self.row_slot[:batch], self.row_pos[:batch]))
+        ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
+        h, d = self.model.hidden(tokens, ctx)
+        logits = self.model.logits(h, d, None)
+        self._choose(logits, slots, self.out_tokens[:batch])
+        ops.advance(self.cache.seq_lens, slots, cu)
+
+    def _set_composition(self, slots: Sequence[int]) -> None:
+        key = tuple(slots)
+        if key == self._composition:
+            return
+        stage = self._stage[self._ring_next]
+        stage[:len(slots)] = torch.tensor(list(slots), dtype=torch.int32)
+        self.slots_buf[:len(slots)].copy_(stage[:len(slots)], non_blocking=True)
+        self._composition = key
+
+    def _capture(self, batch: int) -> None:
+        """Warm the program up on the scratch slot (it advances nothing that lives), then
+        record it."""
+        scratch = torch.full((batch,), self._scratch_slot, dtype=torch.int32, device=self.device)
+        self.slots_buf[:batch].copy_(scratch)
+        self._composition = None
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.cache.seq_lens[self._scratch_slot] = 0
+                self._decode_program(batch)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._decode_program(batch)
+        self.cache.seq_lens[self._scratch_slot] = 0
+        torch.cuda.synchronize()
+        self.graphs[batch] = graph
+
+    def launch_decode(self, slots: Sequence[int]) -> _Handle:
+        batch = len(slots)
+        if self.use_graphs and batch not in self.graphs:
+            self._capture(batch)
+        self._set_composition(slots)
+        if self.use_graphs:
+            self.graphs[batch].replay()
+        else:
+            self._decode_program(batch)
+        self.cache.commit(list(slots), [1] * batch)
+        return self._send(self.out_tokens, batch)
+
+    def fetch(self, handle: _Handle) -> List[int]:
+        handle.event.synchronize()
+        return handle.buffer[:handle.count].tolist()
+
+
+def _as_i64(seed: int) -> int:
+    seed &= 0xFFFFFFFFFFFFFFFF
+    return seed - (1 << 64) if seed >= (1 << 63) else seed

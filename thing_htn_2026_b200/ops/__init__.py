@@ -48,7 +48,8 @@ _SIGNATURES = {
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "thn_scatter_i32": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p],
+                          c_void_p, c_void_p, c_int, c_void_p],
+    "thn_gather_i32": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
 }
 
 _lib = None
@@ -301,10 +302,15 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
 
 def choose_tokens(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
                   seed: Optional[torch.Tensor] = None, stream_id: Optional[torch.Tensor] = None,
-                  step: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  step: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  slots: Optional[torch.Tensor] = None, last_token: Optional[torch.Tensor] = None,
+                  bump_step: bool = False) -> torch.Tensor:
     """logits float32 [rows, vocab] -> int32 [rows].  Rows with temperature 0 (or no
     temperature tensor at all) take the argmax, lowest index on ties; others are drawn
-    from softmax(logits / T) with Philox noise keyed by (seed, stream, step) of the row."""
+    from softmax(logits / T) with Philox noise keyed by (seed, stream, step) of the row.
+    With ``slots`` the per-row values are per-sequence state indexed by ``slots[row]``;
+    ``last_token`` (same indexing) also receives the choice; ``bump_step`` increments the
+    step counter after use."""
     _need(logits, "choose_tokens logits", torch.float32)
     rows, vocab = logits.shape
     if out is None:
@@ -315,12 +321,21 @@ def choose_tokens(logits: torch.Tensor, temperature: Optional[torch.Tensor] = No
         _need(stream_id, "stream", torch.int32)
         _need(step, "step", torch.int32)
     _call("thn_choose_tokens", _ptr(out), _ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature),
-          _ptr(seed), _ptr(stream_id), _ptr(step), _stream())
+          _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(slots), _ptr(last_token), int(bump_step), _stream())
+    return out
+
+
+def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(src, "gather_i32 src", torch.int32)
+    _need(index, "gather_i32 index", torch.int32)
+    if out is None:
+        out = torch.empty(index.shape[0], dtype=torch.int32, device=src.device)
+    _call("thn_gather_i32", _ptr(out), _ptr(src), _ptr(index), index.shape[0], _stream())
     return out
 
 
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "add_rmsnorm", "advance",
-    "attention", "attention_generic", "choose_tokens", "gather_rows", "lib", "linear", "new_error_word",
+    "attention", "attention_generic", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
