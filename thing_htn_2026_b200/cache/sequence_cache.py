@@ -85,8 +85,10 @@ class SequenceCache:
 
         self.book = CacheBook([GroupBook(spec.window, n_pages) for spec in self.kv_specs], page_size,
                               self.max_slots, self.max_pages_per_seq)
+        # Zeroed once: pages are never cleared afterwards, but what lies beyond a sequence's
+        # length must stay finite (a masked key's weight is 0, and 0 * NaN would poison V).
         self.kv_storage = [
-            torch.empty((counts[("kv", g)], n_pages, 2, spec.n_kv, page_size, spec.head_dim), dtype=dtype,
+            torch.zeros((counts[("kv", g)], n_pages, 2, spec.n_kv, page_size, spec.head_dim), dtype=dtype,
                         device=self.device)
             for g, spec in enumerate(self.kv_specs)
         ]

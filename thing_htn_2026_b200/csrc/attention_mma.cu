@@ -1,0 +1,532 @@
+// Tensor-core attention over the paged cache for bfloat16: a flash kernel for steps that
+// bring several tokens per sequence (prompts), and a split-KV kernel with a merge pass for
+// single-token steps (flash decoding).  Scores, softmax and the output accumulate in
+// float32; the un-normalised probabilities are rounded to bfloat16 before they multiply V
+// (engine/kernels/torch_ref.py:219-225).  The reference's counterparts: flash SDPA for
+// prompts (engine/engine.py:1123-1131) and engine/kernels/attention.py:115-275 for decode.
+//
+// Both kernels work on tiles of 64 keys, which is the cache's page size: a tile of one
+// head is 64 * head_dim contiguous values.  Tiles reach shared memory with 16-byte
+// cp.async copies; rows are padded by 16 bytes so that ldmatrix reads do not collide.
+// Instantiated for head sizes 64 and 128; other sizes use the generic kernel.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTile = 64;        // keys per tile == page size
+constexpr int kThreads = 128;    // 4 warps
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(smem)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies a [rows_total=64][D] tile (contiguous in global memory) into padded shared rows.
+template <int D>
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16* smem, const __nv_bfloat16* gmem) {
+    constexpr int kChunksPerRow = D / 8, kPitch = D + 8;
+#pragma unroll
+    for (int c = threadIdx.x; c < kTile * kChunksPerRow; c += kThreads) {
+        const int row = c / kChunksPerRow, col = (c % kChunksPerRow) * 8;
+        cp_async16(smem + row * kPitch + col, gmem + row * D + col);
+    }
+}
+
+// One warp: S[16 x NK*8] = Q[16 x D] K^T for NK key blocks of 8 starting at key_block0.
+template <int D, int NK>
+__device__ __forceinline__ void qk_tile(float (&s)[NK][4], const uint32_t (&qf)[D / 16][4], const __nv_bfloat16* k_smem,
+                                        int key_block0, int lane) {
+    constexpr int kPitch = D + 8;
+#pragma unroll
+    for (int n = 0; n < NK; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NK; n += 2) {
+            uint32_t b[4];
+            const int key = (key_block0 + n + (lane >> 4)) * 8 + (lane & 7);
+            ldmatrix_x4(b, k_smem + key * kPitch + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[n], qf[kk], b[0], b[1]);
+            mma_bf16(s[n + 1], qf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// One warp: O[16 x D] += P[16 x NK*8] V for the same key blocks.  P comes as bf16 A fragments.
+template <int D, int NK>
+__device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const uint32_t (&pf)[NK / 2][4],
+                                        const __nv_bfloat16* v_smem, int key_block0, int lane) {
+    constexpr int kPitch = D + 8;
+#pragma unroll
+    for (int kk = 0; kk < NK / 2; ++kk) {
+#pragma unroll
+        for (int nd = 0; nd < D / 8; nd += 2) {
+            uint32_t b[4];
+            const int key = (key_block0 + 2 * kk) * 8 + ((lane >> 3) & 1) * 8 + (lane & 7);
+            ldmatrix_x4_trans(b, v_smem + key * kPitch + (nd + (lane >> 4)) * 8);
+            mma_bf16(o[nd], pf[kk], b[0], b[1]);
+            mma_bf16(o[nd + 1], pf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// Online-softmax state of the two rows a thread owns (row g = lane / 4 and row g + 8), in
+// the log2 domain.  l holds this thread's share of the row sum until finish().
+struct RowState {
+    float m[2], l[2];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+    }
+};
+
+// Masks (done by the caller), rescales and exponentiates one S tile in place, produces P
+// fragments and rescales O.
+template <int D, int NK>
+__device__ __forceinline__ void softmax_tile(float (&s)[NK][4], RowState& st, float (&o)[D / 8][4],
+                                             uint32_t (&pf)[NK / 2][4]) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < NK; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * r], s[n][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m[r], mx);
+        const float base = m_new == -INFINITY ? 0.f : m_new;       // a row with no visible key yet
+        const float corr = exp2f(st.m[r] - base);                    // exp2(-inf) = 0 on first use
+        st.m[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < NK; ++n) {
+            s[n][2 * r] = exp2f(s[n][2 * r] - base);
+            s[n][2 * r + 1] = exp2f(s[n][2 * r + 1] - base);
+            sum += s[n][2 * r] + s[n][2 * r + 1];
+        }
+        st.l[r] = st.l[r] * corr + sum;
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd) {
+            o[nd][2 * r] *= corr;
+            o[nd][2 * r + 1] *= corr;
+        }
+    }
+#pragma unroll
+    for (int kk = 0; kk < NK / 2; ++kk) {
+        pf[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pf[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pf[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pf[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
+}
+
+// ------------------------------------------------------------------ several tokens per sequence
+
+// One block: 64 consecutive rows of one sequence (tile_row0 .. +64, clipped to the sequence)
+// for one query head; warp w owns rows 16w .. 16w+15.
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
+    __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const int* __restrict__ tile_row0,
+    const int* __restrict__ tile_rows, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv,
+    int n_q, float scale_log2, int window, int* __restrict__ err) {
+    constexpr int kPitch = D + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][kPitch]
+    __nv_bfloat16* k_smem = q_smem + kTile * kPitch;                               // [2][64][kPitch]
+    __nv_bfloat16* v_smem = k_smem + 2 * kTile * kPitch;                           // [2][64][kPitch]
+
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int row0 = tile_row0[tile], n_rows = tile_rows[tile];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int kvh = h / (n_q / kv.n_kv);
+    const int pos0 = row_pos[row0];                   // rows of a tile are consecutive positions
+    const int pos_last = pos0 + n_rows - 1;
+    const int* pages = kv.block_table + (size_t)row_slot[row0] * kv.bt_stride;
+
+    // Q tile -> shared (rows past the sequence are zero)
+    for (int c = threadIdx.x; c < kTile * (D / 8); c += kThreads) {
+        const int r = c / (D / 8), col = (c % (D / 8)) * 8;
+        if (r < n_rows)
+            cp_async16(q_smem + r * kPitch + col, q + ((size_t)(row0 + r) * n_q + h) * D + col);
+        else
+            *reinterpret_cast<uint4*>(q_smem + r * kPitch + col) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+
+    int first_key = 0;
+    if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
+    const int t_first = first_key / kTile, t_last = pos_last / kTile;
+
+    auto issue = [&](int t, int stage) {
+        const int page = pages[t];
+        if (page < 0) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+        } else {
+            const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
+            load_tile_async<D>(k_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 0, kvh, 0));
+            load_tile_async<D>(v_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 1, kvh, 0));
+        }
+        cp_async_commit();
+    };
+    issue(t_first, 0);
+
+    cp_async_wait<1>();          // Q has landed
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], q_smem + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kPitch + kk * 16 + (lane >> 4) * 8);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
+    RowState st;
+    st.init();
+    const int g = lane >> 2, tq = lane & 3;
+    const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};
+
+    for (int t = t_first; t <= t_last; ++t) {
+        const int stage = (t - t_first) & 1;
+        if (t < t_last) issue(t + 1, stage ^ 1); else cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key0 = t * kTile;
+        // A warp whose rows all lie before this tile has nothing to see in it.
+        const bool warp_active = key0 <= pos0 + warp * 16 + 15;
+        if (warp_active) {
+            float s[8][4];
+            qk_tile<D, 8>(s, qf, k_smem + stage * kTile * kPitch, 0, lane);
+            const bool need_mask = key0 + kTile - 1 > pos0 + warp * 16 || (window > 0 && key0 < pos0 + warp * 16 + 15 - window + 1);
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float v = s[n][i] * scale_log2;
+                    if (need_mask) {
+                        const int key = key0 + n * 8 + tq * 2 + (i & 1);
+                        const int p = my_pos[i >> 1];
+                        if (key > p || (window > 0 && key <= p - window)) v = -INFINITY;
+                    }
+                    s[n][i] = v;
+                }
+            uint32_t pf[4][4];
+            softmax_tile<D, 8>(s, st, o, pf);
+            pv_tile<D, 8>(o, pf, v_smem + stage * kTile * kPitch, 0, lane);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = warp * 16 + g + 8 * r;
+        if (row < n_rows) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = out + ((size_t)(row0 + row) * n_q + h) * D;
+#pragma unroll
+            for (int nd = 0; nd < D / 8; ++nd)
+                *reinterpret_cast<uint32_t*>(dst + nd * 8 + tq * 2) = pack_bf16(o[nd][2 * r] * inv, o[nd][2 * r + 1] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ one token per sequence
+
+// One block: (sequence b, kv head, split).  The G query heads of the kv head are the rows
+// of one 16-row tile.  The block walks the 64-key tiles of its split; warp w takes keys
+// 16w .. 16w+15 of every tile and keeps its own running state; the four states are merged
+// at the end.  With n_splits == 1 the block writes the output; otherwise it writes its
+// partial (max, sum, un-normalised output) to scratch for the merge kernel.
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_decode_kernel(
+    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+    PagedKV kv, int n_q, int n_splits, float scale_log2, int window, int* __restrict__ err) {
+    constexpr int kPitch = D + 8, kStages = 3;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kPitch]
+    __nv_bfloat16* k_smem = q_smem + 16 * kPitch;                                   // [kStages][64][kPitch]
+    __nv_bfloat16* v_smem = k_smem + kStages * kTile * kPitch;
+
+    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = n_q / kv.n_kv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = row_pos[b];
+    const int* pages = kv.block_table + (size_t)row_slot[b] * kv.bt_stride;
+
+    int first_key = 0;
+    if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
+    const int t_first = first_key / kTile, t_last = pos / kTile;
+    const int n_tiles = t_last - t_first + 1;
+    const int per_split = (n_tiles + n_splits - 1) / n_splits;
+    const int t_begin = t_first + split * per_split;
+    const int t_end = min(t_begin + per_split, t_last + 1);      // exclusive; may be <= t_begin (empty split)
+
+    for (int c = threadIdx.x; c < 16 * (D / 8); c += kThreads) {
+        const int r = c / (D / 8), col = (c % (D / 8)) * 8;
+        if (r < G)
+            cp_async16(q_smem + r * kPitch + col, q + ((size_t)b * n_q + kvh * G + r) * D + col);
+        else
+            *reinterpret_cast<uint4*>(q_smem + r * kPitch + col) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+
+    auto issue = [&](int t, int stage) {
+        if (t < t_end) {
+            const int page = pages[t];
+            if (page < 0) {
+                if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            } else {
+                const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
+                load_tile_async<D>(k_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 0, kvh, 0));
+                load_tile_async<D>(v_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 1, kvh, 0));
+            }
+        }
+        cp_async_commit();
+    };
+    issue(t_begin, 0);
+    issue(t_begin + 1, 1);
+
+    cp_async_wait<2>();          // Q has landed
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * kPitch + kk * 16 + (lane >> 4) * 8);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
+    RowState st;
+    st.init();
+    const int tq = lane & 3;
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) % kStages;
+        issue(t + 2, (stage + 2) % kStages);
+        cp_async_wait<2>();
+        __syncthreads();
+        const int key0 = t * kTile + warp * 16;
+        float s[2][4];
+        qk_tile<D, 2>(s, qf, k_smem + stage * kTile * kPitch, warp * 2, lane);
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = key0 + n * 8 + tq * 2 + (i & 1);
+                const bool visible = key <= pos && key >= first_key;
+                s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
+            }
+        uint32_t pf[1][4];
+        softmax_tile<D, 2>(s, st, o, pf);
+        pv_tile<D, 2>(o, pf, v_smem + stage * kTile * kPitch, warp * 2, lane);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // Merge the four warps through shared memory (the tile buffers are free now).
+    float* m_smem = reinterpret_cast<float*>(k_smem);           // [4][16]
+    float* l_smem = m_smem + 64;                                // [4][16]
+    float* o_smem = l_smem + 64;                                // [4][16][D]
+    const int g = lane >> 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float l = st.l[r];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = g + 8 * r;
+        if (tq == 0) {
+            m_smem[warp * 16 + row] = st.m[r];
+            l_smem[warp * 16 + row] = l;
+        }
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd) {
+            o_smem[(warp * 16 + row) * D + nd * 8 + tq * 2] = o[nd][2 * r];
+            o_smem[(warp * 16 + row) * D + nd * 8 + tq * 2 + 1] = o[nd][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * D; e += kThreads) {
+        const int row = e / D, d = e % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, m_smem[w * 16 + row]);
+        float l = 0.f, acc = 0.f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float wgt = exp2f(m_smem[w * 16 + row] - m);
+                l += l_smem[w * 16 + row] * wgt;
+                acc += o_smem[(w * 16 + row) * D + d] * wgt;
+            }
+        }
+        const size_t head = (size_t)b * n_q + kvh * G + row;
+        if (n_splits == 1) {
+            out[head * D + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            part_o[(head * n_splits + split) * D + d] = acc;
+            if (d == 0) {
+                part_ml[(head * n_splits + split) * 2] = m;
+                part_ml[(head * n_splits + split) * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// out[head] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m); splits are combined in
+// ascending order.
+__global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                       const float* __restrict__ part_ml, int n_splits, int D) {
+    const size_t head = blockIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(head * n_splits + s) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float l = 0.f, acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(head * n_splits + s) * 2];
+            if (ms == -INFINITY) continue;
+            const float wgt = exp2f(ms - m);
+            l += part_ml[(head * n_splits + s) * 2 + 1] * wgt;
+            acc += part_o[(head * n_splits + s) * D + d] * wgt;
+        }
+        out[head * D + d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+template <int D> constexpr size_t prefill_smem() { return (size_t)(kTile + 4 * kTile) * (D + 8) * 2; }
+template <int D> constexpr size_t decode_smem() { return (size_t)(16 + 6 * kTile) * (D + 8) * 2; }
+
+template <int D>
+int launch_prefill(void* out, const void* q, const int* tile_row0, const int* tile_rows, int n_tiles,
+                   const int* row_slot, const int* row_pos, PagedKV kv, int n_q, float scale, int window, int* err,
+                   cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)prefill_smem<D>());
+        if (e != cudaSuccess) {
+            thn_set_error("attention_prefill: cannot reserve %zu bytes of shared memory: %s", prefill_smem<D>(),
+                          cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid(n_tiles, n_q);
+    attention_prefill_kernel<D><<<grid, kThreads, prefill_smem<D>(), stream>>>(
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
+        scale * kLog2e, window, err);
+    return thn_launch_status("attention_prefill");
+}
+
+template <int D>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
+                  PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* err,
+                  cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)decode_smem<D>());
+        if (e != cudaSuccess) {
+            thn_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s", decode_smem<D>(),
+                          cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid(n_seqs, kv.n_kv, n_splits);
+    attention_decode_kernel<D><<<grid, kThreads, decode_smem<D>(), stream>>>(
+        (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
+        scale * kLog2e, window, err);
+    int status = thn_launch_status("attention_decode");
+    if (status != THN_OK || n_splits == 1) return status;
+    attention_merge_kernel<<<n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml,
+                                                                            n_splits, D);
+    return thn_launch_status("attention_merge");
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernels take this shape (bfloat16 only), else 0.
+THN_API int thn_attention_mma_supported(int head_dim, int page_size, int n_q, int n_kv) {
+    return (head_dim == 64 || head_dim == 128) && page_size == kTile && n_kv > 0 && n_q % n_kv == 0 &&
+           n_q / n_kv <= 16;
+}
+
+// Rows of a step that brings one or more tokens per sequence.  tile_row0[i] is the first
+// packed row of tile i, tile_rows[i] (1..64) the number of its rows; the rows of a tile are
+// consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.
+THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
+                                       int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,
+                                       const int* block_table, int bt_stride, int n_kv, int page_size, int head_dim,
+                                       int n_q, float scale, int window, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0, "attention_prefill: bad sizes");
+    THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
+                       "attention_prefill: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
+                       head_dim, page_size, n_q, n_kv);
+    if (n_tiles == 0) return THN_OK;
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
+    if (head_dim == 64)
+        return launch_prefill<64>(out, q, tile_row0, tile_rows, n_tiles, row_slot, row_pos, kv, n_q, scale, window, err, stream);
+    return launch_prefill<128>(out, q, tile_row0, tile_rows, n_tiles, row_slot, row_pos, kv, n_q, scale, window, err, stream);
+}
+
+// Scratch floats needed by thn_attention_decode_bf16 for n_splits > 1: partial outputs
+// [n_seqs * n_q * n_splits * head_dim] followed by (max, sum) pairs [n_seqs * n_q * n_splits * 2].
+THN_API long long thn_attention_decode_scratch_floats(int n_seqs, int n_q, int n_splits, int head_dim) {
+    if (n_splits <= 1) return 0;
+    return (long long)n_seqs * n_q * n_splits * (head_dim + 2);
+}
+
+// One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
+THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
+                                      const void* kv_base, const int* block_table, int bt_stride, int n_kv,
+                                      int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
+                                      int window, float* scratch, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
+    THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
+                       "attention_decode: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
+                       head_dim, page_size, n_q, n_kv);
+    THN_CHECK_ARG(n_splits == 1 || scratch != nullptr, "attention_decode: %d splits need scratch memory", n_splits);
+    if (n_seqs == 0) return THN_OK;
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
+    if (head_dim == 64)
+        return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
+    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
+}

@@ -60,14 +60,25 @@ class StepRunner:
                 want_rows.append(start + w)
         self.cache.prepare(slots, counts)
 
-        flat = [t for e in entries for t in e.tokens] + cu + slots + want_rows
-        packed = torch.tensor(flat, dtype=torch.int32).to(self.device)
-        tokens = packed[:n_rows]
-        cu_dev = packed[n_rows:n_rows + len(cu)]
-        slots_dev = packed[n_rows + len(cu):n_rows + len(cu) + len(slots)]
-        want_dev = packed[n_rows + len(cu) + len(slots):]
+        tile_row0: List[int] = []
+        tile_rows: List[int] = []
+        if max(counts) > 1:
+            for start, c in zip(cu, counts):
+                for r in range(0, c, 64):
+                    tile_row0.append(start + r)
+                    tile_rows.append(min(64, c - r))
+
+        parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows, tile_row0, tile_rows]
+        packed = torch.tensor([x for part in parts for x in part], dtype=torch.int32).to(self.device)
+        views, at = [], 0
+        for part in parts:
+            views.append(packed[at:at + len(part)])
+            at += len(part)
+        tokens, cu_dev, slots_dev, want_dev, tile_row0_dev, tile_rows_dev = views
 
         rows = ops.step_rows(cu_dev, slots_dev, self.cache.seq_lens, n_rows, max(counts))
+        if tile_row0:
+            rows.tile_row0, rows.tile_rows, rows.n_tiles = tile_row0_dev, tile_rows_dev, len(tile_row0)
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
         h, d = self.model.hidden(tokens, ctx)
         if want_rows:

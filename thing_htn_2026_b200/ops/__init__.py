@@ -50,6 +50,11 @@ _SIGNATURES = {
     "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_int, c_void_p],
     "thn_gather_i32": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
+    "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -63,11 +68,18 @@ def lib():
             fn = getattr(loaded, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        loaded.thn_attention_decode_scratch_floats.restype = c_longlong
         _lib = loaded
     return _lib
 
 
+launch_count = 0   # kernels of this library launched (or recorded into a graph) so far
+
+
 def _call(name: str, *args) -> None:
+    global launch_count
+    launch_count += 1
     code = getattr(lib(), name)(*args)
     if code:
         raise KernelError(f"{name}: {lib().thn_last_error().decode()} (status {code})")
@@ -126,6 +138,11 @@ class StepRows:
     n_rows: int
     n_seqs: int
     max_q_len: int           # longest run of rows of one sequence (host knowledge)
+    # Tiles of at most 64 consecutive rows of one sequence (first packed row, row count), for
+    # kernels that work on row tiles; None when every sequence brings one row.
+    tile_row0: Optional[torch.Tensor] = None
+    tile_rows: Optional[torch.Tensor] = None
+    n_tiles: int = 0
 
 
 def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Tensor, n_rows: int,
@@ -294,7 +311,59 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
               err: torch.Tensor) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
     own keys).  Chooses the kernel by dtype, head size and step shape."""
+    if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+        if rows.max_q_len == 1:
+            return attention_decode_bf16(q, rows, kv, n_q, scale, window, err)
+        if rows.tile_row0 is not None:
+            return attention_prefill_bf16(q, rows, kv, n_q, scale, window, err)
     return attention_generic(q, rows, kv, n_q, scale, window, err)
+
+
+def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+                           window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+    """Tensor-core flash attention for steps with several tokens per sequence."""
+    _need(q, "attention q", torch.bfloat16)
+    out = torch.empty_like(q)
+    _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(rows.tile_row0), _ptr(rows.tile_rows),
+          rows.n_tiles, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
+          kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
+          _ptr(err), _stream())
+    return out
+
+
+_sm_count = {}
+
+
+def decode_splits(n_seqs: int, n_kv: int, device) -> int:
+    """Splits of the key range per (sequence, kv head) so that a single-token step fills the
+    GPU about twice over.  It depends on the batch only, never on the lengths, so a captured
+    step stays valid while the sequences grow."""
+    index = torch.device(device).index or 0
+    if index not in _sm_count:
+        _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    want = -(-2 * _sm_count[index] // max(1, n_seqs * n_kv))
+    return max(1, min(32, want))
+
+
+def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+                          window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
+                          scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
+    through float32 scratch memory, which is allocated here unless given."""
+    _need(q, "attention q", torch.bfloat16)
+    n_seqs = rows.n_rows
+    if n_splits is None:
+        n_splits = decode_splits(n_seqs, kv.n_kv, q.device)
+    need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
+    if need and scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if need and scratch.numel() < need:
+        raise KernelError(f"attention_decode: scratch has {scratch.numel()} floats, {need} needed")
+    out = torch.empty_like(q)
+    _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
+          _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(err), _stream())
+    return out
 
 
 # ------------------------------------------------------------------ token choice
@@ -336,6 +405,6 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "add_rmsnorm", "advance",
-    "attention", "attention_generic", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
+    "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
