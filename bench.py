@@ -159,6 +159,8 @@ def run_ours(args):
                 time.sleep(0.3)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
+            if args.profiler_range and sample_clocks:
+                torch.cuda.profiler.start()
             start.record()
             handles = []
             for _ in range(steps):
@@ -167,6 +169,8 @@ def run_ours(args):
                     backend.fetch(handles.pop(0))
             end.record()
             torch.cuda.synchronize()
+            if args.profiler_range and sample_clocks:
+                torch.cuda.profiler.stop()
             clocks = sampler.stop() if sampler else None
             ms = start.elapsed_time(end) / steps
             ctx_mean = PROMPT + warmup + (steps - 1) / 2.0
@@ -287,6 +291,9 @@ def main():
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    parser.add_argument("--profiler-range", action="store_true",
+                        help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu "
+                             "--profile-from-start off)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")

@@ -1,0 +1,118 @@
+"""Times the kernels of a decode step one by one at the Qwen3-4B layer sizes, each on cold
+operands (the weights rotate through more copies than the L2 cache holds), with CUDA
+events, and prints achieved GB/s beside the vendor library's product on the same shape.
+
+    python kernel_bench.py [--batch 8] [--context 640] [--reps 20]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch  # noqa: E402
+
+H, I, V, NQ, NKV, D = 2560, 9728, 151936, 32, 8, 128
+L2_BYTES = 126 * 2 ** 20
+
+
+def time_cold(make_call, n_variants, reps):
+    """make_call(i) runs the op on operand set i; sets rotate so that each run reads cold data."""
+    # The calls are recorded into one CUDA graph and replayed, so that the time is the
+    # device's (back-to-back kernels, as in a decode step) and not the host's launch cost.
+    for i in range(min(3, n_variants)):
+        make_call(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for r in range(reps):
+            make_call(r % n_variants)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) / reps)
+    return sorted(times)[len(times) // 2] * 1e3   # median per call, microseconds
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=640)
+    parser.add_argument("--reps", type=int, default=20)
+    args = parser.parse_args()
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache
+    dev = "cuda:0"
+    m = args.batch
+    results = {}
+
+    shapes = {"qkv": ((NQ + 2 * NKV) * D, H), "o": (H, NQ * D), "gate_up": (2 * I, H), "down": (H, I),
+              "lm_head": (V, H)}
+    for name, (n, k) in shapes.items():
+        copies = max(2, int(2 * L2_BYTES / (n * k * 2)) + 1)
+        weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        nbytes = n * k * 2
+        entry = {"bytes": nbytes, "copies": copies}
+        if ops.lib().thn_gemm_smallm_supported(m, n, k):
+            us = time_cold(lambda i: ops.linear_smallm(x, weights[i]), copies, args.reps)
+            entry["own_us"], entry["own_gbs"] = us, nbytes / us / 1e3
+            entry["span"], entry["slabs"] = ops.smallm_plan(m, n, k, dev)
+        us = time_cold(lambda i: torch.nn.functional.linear(x, weights[i]), copies, args.reps)
+        entry["library_us"], entry["library_gbs"] = us, nbytes / us / 1e3
+        results[f"gemm_{name}_m{m}"] = entry
+        del weights
+
+    # decode attention over `context` cached tokens per sequence
+    ctx = args.context
+    caches = []
+    n_copies = max(2, int(2 * L2_BYTES / (m * ctx * 2 * NKV * D * 2)) + 1)
+    n_copies = min(n_copies, 64)
+    cache = SequenceCache([KVSpec(NKV, D)] * n_copies, max_tokens=m * (ctx + 64), dtype=torch.bfloat16, device=dev,
+                          max_slots=m + 1)
+    slots = cache.open(m)
+    cache.prepare(slots, [ctx] * m)
+    cu = torch.arange(m + 1, dtype=torch.int32, device=dev) * ctx
+    slots_dev = torch.tensor(slots, dtype=torch.int32, device=dev)
+    rows = ops.step_rows(cu, slots_dev, cache.seq_lens, m * ctx, ctx)
+    ops.advance(cache.seq_lens, slots_dev, cu)
+    cache.commit(slots, [ctx] * m)
+    cache.seq_lens -= 1                       # the step's own token sits at position ctx - 1
+    cu1 = torch.arange(m + 1, dtype=torch.int32, device=dev)
+    rows = ops.step_rows(cu1, slots_dev, cache.seq_lens, m, 1)
+    q = torch.randn(m, NQ * D, device=dev, dtype=torch.bfloat16)
+    err = ops.new_error_word(dev)
+    views = [cache.kv_view(e) for e in range(n_copies)]
+    for view in views:
+        view.storage.normal_()
+    nbytes = m * ctx * 2 * NKV * D * 2
+    us = time_cold(lambda i: ops.attention_decode_bf16(q, rows, views[i], NQ, D ** -0.5, None, err), n_copies,
+                   args.reps)
+    results[f"attention_decode_b{m}_ctx{ctx}"] = {"bytes": nbytes, "own_us": us, "own_gbs": nbytes / us / 1e3,
+                                                  "splits": ops.decode_splits(m, NKV, dev)}
+
+    # the small kernels (latency-bound at this size)
+    h = torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+    d = torch.randn(m, H, device=dev, dtype=torch.bfloat16)
+    gain = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    results["add_rmsnorm"] = {"own_us": time_cold(lambda i: ops.add_rmsnorm(h, d, gain, 1e-6), 1, args.reps)}
+    gu = torch.randn(m, 2 * I, device=dev, dtype=torch.bfloat16)
+    results["swiglu"] = {"own_us": time_cold(lambda i: ops.swiglu(gu), 1, args.reps)}
+    logits = torch.randn(m, V, device=dev, dtype=torch.float32)
+    results["choose_tokens"] = {"own_us": time_cold(lambda i: ops.choose_tokens(logits), 1, args.reps)}
+    for name, entry in results.items():
+        print(name, json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in entry.items()}))
+
+
+if __name__ == "__main__":
+    main()

@@ -100,6 +100,43 @@ def test_rope_table_matches_formula():
         assert (t.sin[:3000].cpu() - sin[:, :head_dim // 2]).abs().max() <= 2e-6
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(100, 64), (2560, 4096), (6144, 2560), (77, 640), (19456, 2560), (2560, 9728)])
+def test_gemm_smallm(m, n, k):
+    """The weight-streaming product for few rows against a float64 product, with the work
+    cut for the whole GPU and for odd numbers of warps (tiles shared by 1 to 8 warps); the
+    result does not depend on the cut beyond float32 order, and not at all on the run."""
+    o = ops()
+    x, w = rand((m, k), torch.bfloat16, 40), rand((n, k), torch.bfloat16, 41, 0.05)
+    exact = x.double() @ w.double().t()
+    bound = 2e-6 * k ** 0.5 * max(1.0, exact.abs().max().item())
+    for n_warps in [0, 7, 1000, 100000]:
+        out32 = o.linear_smallm(x.to(DEV), w.to(DEV), torch.float32, n_warps=n_warps)
+        err = (out32.double().cpu() - exact).abs().max().item()
+        assert err <= bound, f"n_warps {n_warps}: error {err:.3e}"
+        out16 = o.linear_smallm(x.to(DEV), w.to(DEV), n_warps=n_warps)
+        assert torch.equal(out16, out32.to(torch.bfloat16)), "bfloat16 output is the float32 sum rounded once"
+        again = o.linear_smallm(x.to(DEV), w.to(DEV), torch.float32, n_warps=n_warps)
+        assert torch.equal(again, out32), "two runs differ: the order of the sum depends on timing"
+    assert o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).dtype == torch.float32
+
+
+def test_consumers_take_split_sums():
+    """Kernels that read a product as partial sums give what they give on the summed tensor."""
+    o = ops()
+    m, n = 5, 200
+    parts = rand((3, m, n), torch.float32, 44).to(DEV)
+    product = o.SplitSum(parts, torch.bfloat16)
+    tensor = o.resolve(product)
+    assert torch.equal(tensor, (parts[0] + parts[1] + parts[2]).to(torch.bfloat16))
+    assert torch.equal(o.swiglu(product), o.swiglu(tensor))
+    h = rand((m, n), torch.bfloat16, 42).to(DEV)
+    h2 = h.clone()
+    gain = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(43))).to(torch.bfloat16).to(DEV)
+    assert torch.equal(o.add_rmsnorm(h, product, gain, 1e-6), o.add_rmsnorm(h2, tensor, gain, 1e-6))
+    assert torch.equal(h, h2)
+
+
 # ----------------------------------------------------------------------------- cache helpers
 
 

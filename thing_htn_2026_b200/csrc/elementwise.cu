@@ -5,6 +5,11 @@
 // normalised value is rounded before the gain), :61-68 (residual add rounded once),
 // :74-88 (silu rounded, product rounded).  Reductions are float32 with an order fixed
 // by the block size, so a row's result does not depend on the batch it is in.
+//
+// Inputs that come from a matrix product may arrive as split-K partial sums (float32
+// [parts, rows, width], see gemm_smallm.cu): the kernel adds the parts in ascending order
+// and rounds the sum to the activation type, which is the value the product would have
+// stored.
 #include <cstdarg>
 #include <cstdio>
 
@@ -56,52 +61,160 @@ THN_API int thn_gather_rows(void* out, const void* table, const int* index, int 
 
 // ------------------------------------------------------------------ RMSNorm
 
-// y = w * rnd(x * rstd), rstd = 1/sqrt(mean(x^2) + eps).  With ADD: h = rnd(h + d) is
-// stored back first and normalised.  One block per row.
+constexpr int kNormThreads = 256;
+constexpr int kNormKeep = 16;   // values a thread keeps in registers between the two passes
+
+// y = w * rnd(v * rstd), rstd = 1/sqrt(mean(v^2) + eps).  v = h, or with a branch output d:
+// v = rnd(h + d), stored back to h first.  One block per row.
 template <typename T, typename WT, bool ADD>
-__global__ void rmsnorm_kernel(T* __restrict__ y, T* __restrict__ h, const T* __restrict__ d,
-                               const WT* __restrict__ w, int width, float eps) {
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ y, T* __restrict__ h,
+                                                               Source<T> d, const WT* __restrict__ w, int width,
+                                                               float eps) {
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * width;
+    float keep[kNormKeep];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < kNormKeep; ++j) {
+        const int i = threadIdx.x + j * kNormThreads;
+        float v = 0.f;
+        if (i < width) {
+            v = to_f32<T>(h[base + i]);
+            if (ADD) {
+                v = rnd<T>(v + d.load(base + i));
+                h[base + i] = from_f32<T>(v);
+            }
+        }
+        keep[j] = v;
+        ss += v * v;
+    }
+    for (int i = threadIdx.x + kNormKeep * kNormThreads; i < width; i += kNormThreads) {
         float v = to_f32<T>(h[base + i]);
         if (ADD) {
-            v = rnd<T>(v + to_f32<T>(d[base + i]));
+            v = rnd<T>(v + d.load(base + i));
             h[base + i] = from_f32<T>(v);
         }
         ss += v * v;
     }
     const float total = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(total / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < kNormKeep; ++j) {
+        const int i = threadIdx.x + j * kNormThreads;
+        if (i < width) y[base + i] = from_f32<T>(to_f32<WT>(w[i]) * rnd<T>(keep[j] * rstd));
+    }
+    for (int i = threadIdx.x + kNormKeep * kNormThreads; i < width; i += kNormThreads) {
         const float v = to_f32<T>(h[base + i]);
         y[base + i] = from_f32<T>(to_f32<WT>(w[i]) * rnd<T>(v * rstd));
     }
 }
 
-template <typename T, typename WT>
-static void launch_rmsnorm(void* y, void* h, const void* d, const void* w, int rows, int width, float eps,
-                           cudaStream_t stream) {
-    const int threads = width >= 2048 ? 512 : 256;
-    if (d)
-        rmsnorm_kernel<T, WT, true><<<rows, threads, 0, stream>>>((T*)y, (T*)h, (const T*)d, (const WT*)w, width, eps);
-    else
-        rmsnorm_kernel<T, WT, false><<<rows, threads, 0, stream>>>((T*)y, (T*)h, nullptr, (const WT*)w, width, eps);
+// The common serving case, bfloat16 rows of up to 8192 values with width % 8 == 0: one
+// 16-byte vector per thread, every load issued before the first use, same arithmetic and
+// rounding as the kernel above.  blockDim depends on the width only.
+template <typename WT, bool ADD>
+__global__ void __launch_bounds__(1024) rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ y,
+                                                                __nv_bfloat16* __restrict__ h,
+                                                                const __nv_bfloat16* __restrict__ d,
+                                                                const WT* __restrict__ w, int width, float eps) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    const int i0 = threadIdx.x * 8;
+    const bool live = i0 < width;
+    uint4 hv = make_uint4(0, 0, 0, 0), dv = make_uint4(0, 0, 0, 0);
+    float gain[8];
+    if (live) {
+        hv = *reinterpret_cast<const uint4*>(h + base + i0);
+        if (ADD) dv = *reinterpret_cast<const uint4*>(d + base + i0);
+        if (sizeof(WT) == 2) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + i0);
+            const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(&wv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gain[j] = __bfloat162float(wb[j]);
+        } else {
+            const float4 w0 = *reinterpret_cast<const float4*>(w + i0);
+            const float4 w1 = *reinterpret_cast<const float4*>(w + i0 + 4);
+            gain[0] = w0.x; gain[1] = w0.y; gain[2] = w0.z; gain[3] = w0.w;
+            gain[4] = w1.x; gain[5] = w1.y; gain[6] = w1.z; gain[7] = w1.w;
+        }
+    }
+    const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&hv);
+    const __nv_bfloat16* db = reinterpret_cast<const __nv_bfloat16*>(&dv);
+    float v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[j] = __bfloat162float(hb[j]);
+        if (ADD) v[j] = rnd<__nv_bfloat16>(v[j] + __bfloat162float(db[j]));
+        ss += v[j] * v[j];
+    }
+    if (ADD && live) {
+        uint4 out;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&out);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16_rn(v[j]);
+        *reinterpret_cast<uint4*>(h + base + i0) = out;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+    if (live) {
+        uint4 out;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&out);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16_rn(gain[j] * rnd<__nv_bfloat16>(v[j] * rstd));
+        *reinterpret_cast<uint4*>(y + base + i0) = out;
+    }
 }
 
-// d == nullptr: y = RMSNorm(h).  Otherwise h is updated in place to rnd(h + d) first.
-THN_API int thn_rmsnorm(void* y, void* h, const void* d, const void* w, int rows, int width, float eps, int dtype,
-                        int w_dtype, cudaStream_t stream) {
+template <typename WT>
+static bool launch_rmsnorm_vec(void* y, void* h, const void* d, const float* d_parts, const void* w, int rows,
+                               int width, float eps, cudaStream_t stream) {
+    if (d_parts || width % 8 || width > 8192 || (((uintptr_t)y | (uintptr_t)h | (uintptr_t)d | (uintptr_t)w) & 15))
+        return false;
+    const int threads = ((width / 8 + 31) / 32) * 32;
+    if (d)
+        rmsnorm_bf16_vec_kernel<WT, true><<<rows, threads, 0, stream>>>(
+            (__nv_bfloat16*)y, (__nv_bfloat16*)h, (const __nv_bfloat16*)d, (const WT*)w, width, eps);
+    else
+        rmsnorm_bf16_vec_kernel<WT, false><<<rows, threads, 0, stream>>>(
+            (__nv_bfloat16*)y, (__nv_bfloat16*)h, nullptr, (const WT*)w, width, eps);
+    return true;
+}
+
+template <typename T, typename WT>
+static void launch_rmsnorm(void* y, void* h, Source<T> d, bool add, const void* w, int rows, int width, float eps,
+                           cudaStream_t stream) {
+    if (add)
+        rmsnorm_kernel<T, WT, true><<<rows, kNormThreads, 0, stream>>>((T*)y, (T*)h, d, (const WT*)w, width, eps);
+    else
+        rmsnorm_kernel<T, WT, false><<<rows, kNormThreads, 0, stream>>>((T*)y, (T*)h, d, (const WT*)w, width, eps);
+}
+
+// y = RMSNorm(h).  With d (a tensor of h's type) or d_parts (n_parts float32 partials, each
+// rows * width): h is updated in place to rnd(h + d) first.
+THN_API int thn_rmsnorm(void* y, void* h, const void* d, const float* d_parts, int n_parts, const void* w, int rows,
+                        int width, float eps, int dtype, int w_dtype, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
     THN_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive, got %g", (double)eps);
+    THN_CHECK_ARG(!(d && d_parts) && (d_parts == nullptr || n_parts >= 1), "rmsnorm: one source for d, please");
     if (rows == 0) return THN_OK;
+    const bool add = d || d_parts;
+    const long long stride = (long long)rows * width;
     if (dtype == THN_F32 && w_dtype == THN_F32)
-        launch_rmsnorm<float, float>(y, h, d, w, rows, width, eps, stream);
-    else if (dtype == THN_BF16 && w_dtype == THN_BF16)
-        launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(y, h, d, w, rows, width, eps, stream);
+        launch_rmsnorm<float, float>(y, h, Source<float>{(const float*)d, d_parts, n_parts, stride}, add, w, rows,
+                                     width, eps, stream);
+    else if (dtype == THN_BF16 && w_dtype == THN_BF16 &&
+             launch_rmsnorm_vec<__nv_bfloat16>(y, h, d, d_parts, w, rows, width, eps, stream)) {
+    } else if (dtype == THN_BF16 && w_dtype == THN_F32 &&
+               launch_rmsnorm_vec<float>(y, h, d, d_parts, w, rows, width, eps, stream)) {
+    } else if (dtype == THN_BF16 && w_dtype == THN_BF16)
+        launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(
+            y, h, Source<__nv_bfloat16>{(const __nv_bfloat16*)d, d_parts, n_parts, stride}, add, w, rows, width, eps,
+            stream);
     else if (dtype == THN_BF16 && w_dtype == THN_F32)
-        launch_rmsnorm<__nv_bfloat16, float>(y, h, d, w, rows, width, eps, stream);
+        launch_rmsnorm<__nv_bfloat16, float>(
+            y, h, Source<__nv_bfloat16>{(const __nv_bfloat16*)d, d_parts, n_parts, stride}, add, w, rows, width, eps,
+            stream);
     else
         THN_CHECK_ARG(false, "rmsnorm: unsupported dtypes activation=%d gain=%d", dtype, w_dtype);
     return thn_launch_status("rmsnorm");
@@ -111,32 +224,66 @@ THN_API int thn_rmsnorm(void* y, void* h, const void* d, const void* w, int rows
 
 // out[m, i] = rnd(rnd(g / (1 + exp(-g))) * u), g = gu[m, i], u = gu[m, inter + i].
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int inter) {
+__global__ void swiglu_kernel(T* __restrict__ out, Source<T> gu, long long total, int inter) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
         const long long m = e / inter;
         const int i = (int)(e - m * inter);
-        const float g = to_f32<T>(gu[m * 2 * inter + i]);
-        const float u = to_f32<T>(gu[m * 2 * inter + inter + i]);
+        const float g = gu.load(m * 2 * inter + i);
+        const float u = gu.load(m * 2 * inter + inter + i);
         const float s = rnd<T>(g / (1.0f + expf(-g)));
         out[e] = from_f32<T>(s * u);
     }
 }
 
-THN_API int thn_swiglu(void* out, const void* gu, int rows, int inter, int dtype, cudaStream_t stream) {
+// gu [rows, 2 * inter] as a tensor, or as n_parts float32 partials.
+THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_parts, int rows, int inter, int dtype,
+                       cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
+    THN_CHECK_ARG((gu != nullptr) != (gu_parts != nullptr), "swiglu: one source, please");
     const long long total = (long long)rows * inter;
     if (total == 0) return THN_OK;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const long long stride = 2 * total;
     if (dtype == THN_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gu, total, inter);
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>(
+            (float*)out, Source<float>{(const float*)gu, gu_parts, n_parts, stride}, total, inter);
     else if (dtype == THN_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu,
-                                                                     total, inter);
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            (__nv_bfloat16*)out, Source<__nv_bfloat16>{(const __nv_bfloat16*)gu, gu_parts, n_parts, stride}, total,
+            inter);
     else
         THN_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
     return thn_launch_status("swiglu");
+}
+
+// ------------------------------------------------------------------ partial sums -> tensor
+
+template <typename T>
+__global__ void resolve_kernel(T* __restrict__ out, Source<T> src, long long total) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride)
+        out[e] = from_f32<T>(src.load(e));
+}
+
+// out[e] = rnd(sum over parts), e < total: what the product would have stored.
+THN_API int thn_resolve_parts(void* out, const float* parts, int n_parts, long long total, int dtype,
+                              cudaStream_t stream) {
+    THN_CHECK_ARG(total >= 0 && n_parts >= 1, "resolve_parts: bad sizes");
+    if (total == 0) return THN_OK;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == THN_F32)
+        resolve_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, Source<float>{nullptr, parts, n_parts, total},
+                                                          total);
+    else if (dtype == THN_BF16)
+        resolve_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (__nv_bfloat16*)out, Source<__nv_bfloat16>{nullptr, parts, n_parts, total}, total);
+    else
+        THN_CHECK_ARG(false, "resolve_parts: unknown dtype %d", dtype);
+    return thn_launch_status("resolve_parts");
 }
 
 // ------------------------------------------------------------------ step bookkeeping
@@ -203,7 +350,7 @@ THN_API int thn_rope_table(float* cos_out, float* sin_out, const float* inv_freq
     return thn_launch_status("rope_table");
 }
 
-// ------------------------------------------------------------------ int32 scatter
+// ------------------------------------------------------------------ int32 scatter and gather
 
 // dst[index[i]] = value[i]: block-table cells and per-sequence counters changed by the host.
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const long long* __restrict__ index,

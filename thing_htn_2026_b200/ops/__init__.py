@@ -7,6 +7,7 @@ else, and every product of the 32-bit path, is this library's own kernel.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -35,12 +36,18 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "thn_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "thn_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
-    "thn_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "thn_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_int,
+                    c_void_p],
+    "thn_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "thn_resolve_parts": [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p],
+    "thn_gemm_smallm_supported": [c_int, c_int, c_int],
+    "thn_gemm_smallm_plan": [c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "thn_gemm_smallm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p],
     "thn_step_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_advance": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+    "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -74,6 +81,7 @@ def lib():
     return _lib
 
 
+_sm_count = {}
 launch_count = 0   # kernels of this library launched (or recorded into a graph) so far
 
 
@@ -187,6 +195,46 @@ def gather_rows(table: torch.Tensor, index: torch.Tensor, err: Optional[torch.Te
     return out
 
 
+@dataclass
+class SplitSum:
+    """The output of a matrix product as split-K partial sums: ``parts`` is float32
+    ``[n_parts, rows, width]`` and the product is their sum over the first axis, rounded to
+    ``dtype``.  Kernels that consume a product take this in place of a tensor and do the
+    sum themselves; :func:`resolve` turns it into a tensor."""
+
+    parts: torch.Tensor
+    dtype: torch.dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+
+Product = "torch.Tensor | SplitSum"
+
+
+def _source(value, what: str, dtype: torch.dtype):
+    """(tensor pointer, parts pointer, n_parts) of a product given either way."""
+    if isinstance(value, SplitSum):
+        if value.dtype != dtype:
+            raise KernelError(f"{what}: product is {value.dtype}, expected {dtype}")
+        _need(value.parts, what, torch.float32)
+        return None, _ptr(value.parts), value.parts.shape[0]
+    _need(value, what, dtype)
+    return _ptr(value), None, 0
+
+
+def resolve(value) -> torch.Tensor:
+    """A product as a tensor of its dtype (sums the partials if it came split)."""
+    if not isinstance(value, SplitSum):
+        return value
+    rows, width = value.shape
+    out = torch.empty((rows, width), dtype=value.dtype, device=value.parts.device)
+    _call("thn_resolve_parts", _ptr(out), _ptr(value.parts), value.parts.shape[0], rows * width,
+          DTYPE_CODE[value.dtype], _stream())
+    return out
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
     _need(x, "rmsnorm x")
     _need(gain, "rmsnorm gain")
@@ -194,33 +242,35 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
         raise KernelError(f"rmsnorm: gain has {gain.shape[0]} entries, rows have {x.shape[-1]}")
     y = torch.empty_like(x)
     rows = x.numel() // x.shape[-1]
-    _call("thn_rmsnorm", _ptr(y), _ptr(x), None, _ptr(gain), rows, x.shape[-1], float(eps), _code(x, "rmsnorm"),
-          _code(gain, "rmsnorm gain"), _stream())
+    _call("thn_rmsnorm", _ptr(y), _ptr(x), None, None, 0, _ptr(gain), rows, x.shape[-1], float(eps),
+          _code(x, "rmsnorm"), _code(gain, "rmsnorm gain"), _stream())
     return y
 
 
-def add_rmsnorm(h: torch.Tensor, d: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
-    """h <- round(h + d) in place; returns RMSNorm(h) * gain."""
+def add_rmsnorm(h: torch.Tensor, d, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """h <- round(h + d) in place; returns RMSNorm(h) * gain.  ``d`` is a tensor or a SplitSum."""
     _need(h, "add_rmsnorm h")
-    _need(d, "add_rmsnorm d", h.dtype)
     _need(gain, "add_rmsnorm gain")
-    if d.shape != h.shape or gain.shape[0] != h.shape[-1]:
+    if tuple(d.shape) != tuple(h.shape) or gain.shape[0] != h.shape[-1]:
         raise KernelError(f"add_rmsnorm: shapes h {tuple(h.shape)}, d {tuple(d.shape)}, gain {tuple(gain.shape)}")
+    direct, parts, n_parts = _source(d, "add_rmsnorm d", h.dtype)
     y = torch.empty_like(h)
     rows = h.numel() // h.shape[-1]
-    _call("thn_rmsnorm", _ptr(y), _ptr(h), _ptr(d), _ptr(gain), rows, h.shape[-1], float(eps),
+    _call("thn_rmsnorm", _ptr(y), _ptr(h), direct, parts, n_parts, _ptr(gain), rows, h.shape[-1], float(eps),
           _code(h, "add_rmsnorm"), _code(gain, "add_rmsnorm gain"), _stream())
     return y
 
 
-def swiglu(gu: torch.Tensor) -> torch.Tensor:
-    """gu [rows, 2*I] (gate columns first) -> silu(gate) * up, [rows, I]."""
-    _need(gu, "swiglu")
+def swiglu(gu) -> torch.Tensor:
+    """gu [rows, 2*I] (gate columns first; a tensor or a SplitSum) -> silu(gate) * up, [rows, I]."""
     rows, width = gu.shape
     if width % 2:
         raise KernelError(f"swiglu: width {width} is odd")
-    out = torch.empty((rows, width // 2), dtype=gu.dtype, device=gu.device)
-    _call("thn_swiglu", _ptr(out), _ptr(gu), rows, width // 2, _code(gu, "swiglu"), _stream())
+    dtype = gu.dtype
+    direct, parts, n_parts = _source(gu, "swiglu", dtype)
+    device = gu.parts.device if isinstance(gu, SplitSum) else gu.device
+    out = torch.empty((rows, width // 2), dtype=dtype, device=device)
+    _call("thn_swiglu", _ptr(out), direct, parts, n_parts, rows, width // 2, DTYPE_CODE[dtype], _stream())
     return out
 
 
@@ -236,11 +286,72 @@ def rope_table(cos: torch.Tensor, sin: torch.Tensor, inv_freq: torch.Tensor, fir
 # ------------------------------------------------------------------ matrix products
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16: the
-    vendor library's tensor-core product with float32 accumulation (the reference's
-    choice, engine/engine.py:341-350); ``out_dtype=torch.float32`` keeps the
-    accumulator's precision (used for logits)."""
+def _sm_count_of(device) -> int:
+    index = torch.device(device).index or 0
+    if index not in _sm_count:
+        _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_count[index]
+
+
+# Few-row products go to this library's weight-streaming kernel when the reduction is at
+# least this deep; measured on B200 at 8 rows (kernel_bench.py): it beats the vendor library
+# at K = 4096 and 9728 (9.9 vs 10.3 us, 15.0 vs 20.0 us) and loses at K = 2560 (10.9 vs 7.5 us,
+# 21.9 vs 17.5 us).
+SMALLM_MIN_K = int(os.environ.get("THN_SMALLM_MIN_K", 4096))
+
+_smallm_plans = {}
+_smallm_counters = {}
+
+
+def smallm_plan(m: int, n: int, k: int, device, n_warps: int = 0):
+    """(span, slabs) of the weight-streaming product for a shape; cached."""
+    key = (m <= 8, n, k, n_warps, torch.device(device).index or 0)
+    if key not in _smallm_plans:
+        span = ctypes.c_int(0)
+        slabs = lib().thn_gemm_smallm_plan(m, n, k, _sm_count_of(device), n_warps, ctypes.byref(span))
+        _smallm_plans[key] = (span.value, slabs)
+    return _smallm_plans[key]
+
+
+def _smallm_counter_buffer(n_tiles: int, device) -> torch.Tensor:
+    """Arrival counters, one per 16 weight rows; zero between calls (the kernel resets them)."""
+    index = torch.device(device).index or 0
+    have = _smallm_counters.get(index)
+    if have is None or have.numel() < n_tiles:
+        have = torch.zeros(max(n_tiles, 16384), dtype=torch.int32, device=device)
+        _smallm_counters[index] = have
+    return have
+
+
+def linear_smallm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                  n_warps: int = 0, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The weight-streaming product for few rows (bfloat16 operands, M <= 16, K a multiple of
+    64) -> ``[M, N]`` in bfloat16 or float32.  Tiles shared by several warps go through
+    float32 scratch memory, allocated here unless given.  ``n_warps`` overrides the number
+    of warps the work is cut for (tests)."""
+    _need(x, "linear_smallm x", torch.bfloat16)
+    _need(weight, "linear_smallm weight", torch.bfloat16)
+    m, k = x.shape
+    n = weight.shape[0]
+    span, slabs = smallm_plan(m, n, k, x.device, n_warps)
+    if slabs and scratch is None:
+        scratch = torch.empty(slabs * m * n, dtype=torch.float32, device=x.device)
+    if slabs and scratch.numel() < slabs * m * n:
+        raise KernelError(f"linear_smallm: scratch has {scratch.numel()} floats, {slabs * m * n} needed")
+    counters = _smallm_counter_buffer((n + 15) // 16, x.device) if slabs else None
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _call("thn_gemm_smallm_bf16", _ptr(out), DTYPE_CODE[out_dtype], _ptr(scratch) if slabs else None, _ptr(counters),
+          _ptr(x), _ptr(weight), m, n, k, span, slabs, _stream())
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False):
+    """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
+    rows: this library's weight-streaming kernel.  bfloat16 otherwise: the vendor library's
+    tensor-core product with float32 accumulation (the reference's choice,
+    engine/engine.py:341-350).  ``out_dtype=torch.float32`` keeps the accumulator's
+    precision (used for logits).  With ``split_ok`` the result may be a :class:`SplitSum`
+    for a consuming kernel to add up; otherwise it is always a tensor."""
     _need(x, "linear x")
     _need(weight, "linear weight", x.dtype)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -251,6 +362,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return out
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: dtype {x.dtype} is not supported")
+    if x.shape[1] >= SMALLM_MIN_K and lib().thn_gemm_smallm_supported(x.shape[0], weight.shape[0], x.shape[1]):
+        return linear_smallm(x, weight, out_dtype or torch.bfloat16)
     if out_dtype in (None, torch.bfloat16):
         return torch.nn.functional.linear(x, weight)
     return torch.mm(x, weight.t(), out_dtype=out_dtype)
@@ -277,23 +390,24 @@ class RotaryTables:
     rotary_dim: int
 
 
-def qk_norm_rope_cache(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
                        eps: float, rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int,
                        write_cache: bool, err: torch.Tensor) -> torch.Tensor:
-    _need(qkv, "qk_norm_rope_cache qkv")
+    """qkv (a tensor or a SplitSum) -> q, normalised and rotated; K and V go to the cache."""
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
-    if qkv.shape != (rows.n_rows, width):
+    if tuple(qkv.shape) != (rows.n_rows, width):
         raise KernelError(f"qk_norm_rope_cache: qkv is {tuple(qkv.shape)}, expected {(rows.n_rows, width)}")
     if kv.storage.dtype != qkv.dtype:
         raise KernelError(f"qk_norm_rope_cache: cache is {kv.storage.dtype}, activations {qkv.dtype}")
-    q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=qkv.dtype, device=qkv.device)
-    w_code = _code(q_gain, "qk gains") if q_gain is not None else _code(qkv, "qkv")
-    _call("thn_qk_norm_rope_cache", _ptr(q), _ptr(qkv), _ptr(q_gain), _ptr(k_gain), w_code, float(eps),
+    direct, parts, n_parts = _source(qkv, "qk_norm_rope_cache qkv", qkv.dtype)
+    q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=qkv.dtype, device=kv.storage.device)
+    w_code = _code(q_gain, "qk gains") if q_gain is not None else DTYPE_CODE[qkv.dtype]
+    _call("thn_qk_norm_rope_cache", _ptr(q), direct, parts, n_parts, _ptr(q_gain), _ptr(k_gain), w_code, float(eps),
           _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
           rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
           _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, rows.n_rows, n_q, int(write_cache),
-          _code(qkv, "qkv"), _ptr(err), _stream())
+          DTYPE_CODE[qkv.dtype], _ptr(err), _stream())
     return q
 
 
@@ -331,17 +445,11 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int
     return out
 
 
-_sm_count = {}
-
-
 def decode_splits(n_seqs: int, n_kv: int, device) -> int:
     """Splits of the key range per (sequence, kv head) so that a single-token step fills the
     GPU about twice over.  It depends on the batch only, never on the lengths, so a captured
     step stays valid while the sequences grow."""
-    index = torch.device(device).index or 0
-    if index not in _sm_count:
-        _sm_count[index] = torch.cuda.get_device_properties(index).multi_processor_count
-    want = -(-2 * _sm_count[index] // max(1, n_seqs * n_kv))
+    want = -(-2 * _sm_count_of(device) // max(1, n_seqs * n_kv))
     return max(1, min(32, want))
 
 
@@ -404,7 +512,7 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 
 __all__ = [
-    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "add_rmsnorm", "advance",
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_smallm", "resolve", "smallm_plan", "add_rmsnorm", "advance",
     "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -29,4 +29,4 @@ class SwiGLU:
         self.w_down = runtime.tensor(spec, "down_proj")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up)), self.w_down)
+        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up, split_ok=True)), self.w_down, split_ok=True)
