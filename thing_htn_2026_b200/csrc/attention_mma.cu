@@ -530,3 +530,64 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
         return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
     return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
 }
+
+// ------------------------------------------------------------------ no device allocation
+
+#include <mutex>
+
+#include "attention_no_alloc.h"
+
+namespace {
+
+// Scratch of thn_attention_decode_bf16_no_alloc.  In host code this name is only a handle
+// for cudaGetSymbolAddress; the address a kernel can use is looked up once per device.
+static __device__ __align__(256) float g_no_alloc_scratch[THN_NO_ALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_no_alloc_address[kMaxDevices] = {};
+std::mutex g_no_alloc_mutex;
+
+// The device address of the scratch array on the current device, or null with the error set.
+float* no_alloc_scratch_address() {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        thn_set_error("attention_decode_no_alloc: cannot tell the current device (%s)",
+                      e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_address[device] == nullptr) {
+        float* address = nullptr;
+        e = cudaGetSymbolAddress((void**)&address, g_no_alloc_scratch);
+        if (e != cudaSuccess || address == nullptr) {
+            thn_set_error("attention_decode_no_alloc: cudaGetSymbolAddress failed on device %d: %s", device,
+                          cudaGetErrorString(e));
+            return nullptr;
+        }
+        g_no_alloc_address[device] = address;
+    }
+    return g_no_alloc_address[device];
+}
+
+}  // namespace
+
+THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const int* row_slot, const int* row_pos,
+                                               const void* kv_base, const int* block_table, int bt_stride, int n_kv,
+                                               int page_size, int head_dim, int n_seqs, int n_q, int n_splits,
+                                               float scale, int window, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535 && head_dim > 0,
+                  "attention_decode_no_alloc: bad sizes");
+    const long long need = thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, head_dim);
+    THN_CHECK_ARG(need <= THN_NO_ALLOC_SCRATCH_FLOATS,
+                  "attention_decode_no_alloc: %d sequences x %d heads x %d splits x head size %d need %lld floats of "
+                  "scratch, the built-in array holds %d; use fewer splits, or thn_attention_decode_bf16 with "
+                  "scratch of your own", n_seqs, n_q, n_splits, head_dim, need, THN_NO_ALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (need > 0) {
+        scratch = no_alloc_scratch_address();
+        if (scratch == nullptr) return THN_BAD_ARGUMENT;
+    }
+    return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, err, stream);
+}
