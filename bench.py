@@ -159,7 +159,7 @@ def run_ours(args):
                 time.sleep(0.3)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
-            if args.profiler_range and sample_clocks:
+            if args.profiler_range == "decode" and sample_clocks:
                 torch.cuda.profiler.start()
             start.record()
             handles = []
@@ -169,7 +169,7 @@ def run_ours(args):
                     backend.fetch(handles.pop(0))
             end.record()
             torch.cuda.synchronize()
-            if args.profiler_range and sample_clocks:
+            if args.profiler_range == "decode" and sample_clocks:
                 torch.cuda.profiler.stop()
             clocks = sampler.stop() if sampler else None
             ms = start.elapsed_time(end) / steps
@@ -220,15 +220,21 @@ def run_ours(args):
     # prefill of one 2,048-token prompt
     runner = backend.runner
     times = []
-    for rep in range(max(3, min(args.warmup, 5)) + 3):
+    n_prefills = max(3, min(args.warmup, 5)) + 3
+    for rep in range(n_prefills):
         (slot,) = backend.cache.open(1)
         toks = prompts(1, PREFILL_TOKENS)[0]
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        profiled = args.profiler_range == "prefill" and rep == n_prefills - 1
+        if profiled:
+            torch.cuda.profiler.start()
         start.record()
         logits = runner.step([StepEntry(slot, toks, (PREFILL_TOKENS - 1,))], check=False)
         end.record()
         torch.cuda.synchronize()
+        if profiled:
+            torch.cuda.profiler.stop()
         times.append(start.elapsed_time(end))
         backend.cache.close([slot])
     prefill_ms = statistics.median(times[3:])
@@ -291,9 +297,9 @@ def main():
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--profiler-range", action="store_true",
-                        help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu "
-                             "--profile-from-start off)")
+    parser.add_argument("--profiler-range", choices=["decode", "prefill"], default=None,
+                        help="bracket the timed decode steps, or the last prefill, with cudaProfilerStart/Stop "
+                             "(for ncu --profile-from-start off)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")

@@ -163,7 +163,9 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
     __nv_bfloat16* k_smem = q_smem + kTile * kPitch;                               // [2][64][kPitch]
     __nv_bfloat16* v_smem = k_smem + 2 * kTile * kPitch;                           // [2][64][kPitch]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // Later tiles of a sequence see more keys and run longer: start them first, so that the
+    // short ones fill the end of the grid.
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
     const int row0 = tile_row0[tile], n_rows = tile_rows[tile];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (n_q / kv.n_kv);

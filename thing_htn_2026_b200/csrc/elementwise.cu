@@ -236,6 +236,29 @@ __global__ void swiglu_kernel(T* __restrict__ out, Source<T> gu, long long total
     }
 }
 
+// bfloat16 tensor input with inter % 8 == 0: eight values per thread, 16-byte accesses.
+__global__ void swiglu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
+                                       long long total_vecs, int inter_vecs) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vecs; e += stride) {
+        const long long m = e / inter_vecs;
+        const int i = (int)(e - m * inter_vecs);
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + (m * 2 * inter_vecs + i) * 8);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + (m * 2 * inter_vecs + inter_vecs + i) * 8);
+        const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(&gv);
+        const __nv_bfloat16* ub = reinterpret_cast<const __nv_bfloat16*>(&uv);
+        uint4 ov;
+        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float g = __bfloat162float(gb[j]);
+            const float s = rnd<__nv_bfloat16>(g / (1.0f + expf(-g)));
+            ob[j] = __float2bfloat16_rn(s * __bfloat162float(ub[j]));
+        }
+        *reinterpret_cast<uint4*>(out + e * 8) = ov;
+    }
+}
+
 // gu [rows, 2 * inter] as a tensor, or as n_parts float32 partials.
 THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_parts, int rows, int inter, int dtype,
                        cudaStream_t stream) {
@@ -247,6 +270,13 @@ THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_p
     const long long want = (total + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     const long long stride = 2 * total;
+    if (dtype == THN_BF16 && gu && inter % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+        const long long vecs = total / 8;
+        const long long want_vec = (vecs + threads - 1) / threads;
+        swiglu_bf16_vec_kernel<<<(unsigned)(want_vec < 148 * 32 ? want_vec : 148 * 32), threads, 0, stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, vecs, inter / 8);
+        return thn_launch_status("swiglu");
+    }
     if (dtype == THN_F32)
         swiglu_kernel<float><<<blocks, threads, 0, stream>>>(
             (float*)out, Source<float>{(const float*)gu, gu_parts, n_parts, stride}, total, inter);
