@@ -21,6 +21,8 @@ __global__ void attention_generic_kernel(T* __restrict__ out, const T* __restric
                                          const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                          PagedKV kv, int n_rows, int n_q, float scale, int window,
                                          int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= (long long)n_rows * n_q) return;
@@ -90,7 +92,7 @@ static int launch_generic(void* out, const void* q, const int* row_slot, const i
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const int per_lane = (kv.head_dim + 31) / 32;
 #define LAUNCH(N)                                                                                                  \
-    attention_generic_kernel<T, N><<<blocks, warps * 32, 0, stream>>>((T*)out, (const T*)q, row_slot, row_pos, kv, \
+    thn_launch(attention_generic_kernel<T, N>, blocks, warps * 32, 0, stream, (T*)out, (const T*)q, row_slot, row_pos, kv, \
                                                                       n_rows, n_q, scale, window, err)
     if (per_lane <= 1) LAUNCH(1);
     else if (per_lane <= 2) LAUNCH(2);

@@ -157,6 +157,8 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
     __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const int* __restrict__ tile_row0,
     const int* __restrict__ tile_rows, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv,
     int n_q, float scale_log2, int window, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int kPitch = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][kPitch]
@@ -270,13 +272,20 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
 // of one 16-row tile.  The block walks the 64-key tiles of its split; warp w takes keys
 // 16w .. 16w+15 of every tile and keeps its own running state; the four states are merged
 // at the end.  With n_splits == 1 the block writes the output; otherwise it writes its
-// partial (max, sum, un-normalised output) to scratch for the merge kernel.
+// partial (max, sum, un-normalised output) to scratch.  With counters, each block then counts
+// itself in on its (sequence, kv head), and the block that arrives last combines the
+// partials in split order (so the result does not depend on who was last) and writes the
+// output; nobody waits.  Without counters the merge kernel does it.
 template <int D>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
-    PagedKV kv, int n_q, int n_splits, float scale_log2, int window, int* __restrict__ err) {
-    constexpr int kPitch = D + 8, kStages = 3;
+    PagedKV kv, int n_q, int n_splits, float scale_log2, int window, int* __restrict__ counters,
+    int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int kPitch = D + 8, kStages = 2;
+    __shared__ int is_last;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kPitch]
     __nv_bfloat16* k_smem = q_smem + 16 * kPitch;                                   // [kStages][64][kPitch]
@@ -319,9 +328,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         cp_async_commit();
     };
     issue(t_begin, 0);
-    issue(t_begin + 1, 1);
 
-    cp_async_wait<2>();          // Q has landed
+    cp_async_wait<1>();          // Q has landed
     __syncthreads();
     uint32_t qf[D / 16][4];
 #pragma unroll
@@ -339,8 +347,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % kStages;
-        issue(t + 2, (stage + 2) % kStages);
-        cp_async_wait<2>();
+        issue(t + 1, stage ^ 1);
+        cp_async_wait<1>();
         __syncthreads();
         const int key0 = t * kTile + warp * 16;
         float s[2][4];
@@ -401,12 +409,49 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         if (n_splits == 1) {
             out[head * D + d] = __float2bfloat16_rn(acc / l);
         } else {
-            part_o[(head * n_splits + split) * D + d] = acc;
+            __stcg(part_o + (head * n_splits + split) * D + d, acc);
             if (d == 0) {
-                part_ml[(head * n_splits + split) * 2] = m;
-                part_ml[(head * n_splits + split) * 2 + 1] = l;
+                __stcg(part_ml + (head * n_splits + split) * 2, m);
+                __stcg(part_ml + (head * n_splits + split) * 2 + 1, l);
             }
         }
+    }
+    if (n_splits == 1 || counters == nullptr) return;
+
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(counters + b * kv.n_kv + kvh, 1) == n_splits - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[b * kv.n_kv + kvh] = 0;        // ready for the next call
+    // Weights of the splits, one warp per head: lane = split (n_splits <= 32).
+    float* w_smem = reinterpret_cast<float*>(v_smem);            // [16][32]
+    float* l_total = w_smem + 16 * 32;                           // [16]
+    for (int row = warp; row < G; row += 4) {
+        const size_t head = (size_t)b * n_q + kvh * G + row;
+        const float ms = lane < n_splits ? __ldcg(part_ml + (head * n_splits + lane) * 2) : -INFINITY;
+        const float ls = lane < n_splits ? __ldcg(part_ml + (head * n_splits + lane) * 2 + 1) : 0.f;
+        const float m = warp_max(ms);
+        const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - m);
+        const float l = warp_sum(ls * wgt);
+        w_smem[row * 32 + lane] = wgt;
+        if (lane == 0) l_total[row] = l;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * D; e += kThreads) {
+        const int row = e / D, d = e % D;
+        const size_t head = (size_t)b * n_q + kvh * G + row;
+        const float* src = part_o + head * n_splits * D + d;
+        float acc = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {               // eight loads in flight, added in split order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? __ldcg(src + (size_t)(s0 + j) * D) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc += v[j] * w_smem[row * 32 + ((s0 + j) & 31)];
+        }
+        out[head * D + d] = __float2bfloat16_rn(acc / l_total[row]);
     }
 }
 
@@ -414,6 +459,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
 // ascending order.
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, int n_splits, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t head = blockIdx.x;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(head * n_splits + s) * 2]);
@@ -431,7 +478,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
 }
 
 template <int D> constexpr size_t prefill_smem() { return (size_t)(kTile + 4 * kTile) * (D + 8) * 2; }
-template <int D> constexpr size_t decode_smem() { return (size_t)(16 + 6 * kTile) * (D + 8) * 2; }
+template <int D> constexpr size_t decode_smem() { return (size_t)(16 + 4 * kTile) * (D + 8) * 2; }
 
 template <int D>
 int launch_prefill(void* out, const void* q, const int* tile_row0, const int* tile_rows, int n_tiles,
@@ -449,16 +496,13 @@ int launch_prefill(void* out, const void* q, const int* tile_row0, const int* ti
         configured = true;
     }
     dim3 grid(n_tiles, n_q);
-    attention_prefill_kernel<D><<<grid, kThreads, prefill_smem<D>(), stream>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
+    thn_launch(attention_prefill_kernel<D>, grid, kThreads, prefill_smem<D>(), stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
         scale * kLog2e, window, err);
     return thn_launch_status("attention_prefill");
 }
 
 template <int D>
-int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
-                  PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* err,
-                  cudaStream_t stream) {
+int configure_decode() {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -470,13 +514,30 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
         }
         configured = true;
     }
+    return THN_OK;
+}
+
+template <int D>
+int decode_blocks_per_sm() {
+    if (configure_decode<D>() != THN_OK) return 1;
+    int blocks = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D>, kThreads,
+                                                                  decode_smem<D>());
+    return (e == cudaSuccess && blocks > 0) ? blocks : 1;
+}
+
+template <int D>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
+                  PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                  cudaStream_t stream) {
+    int configured = configure_decode<D>();
+    if (configured != THN_OK) return configured;
     dim3 grid(n_seqs, kv.n_kv, n_splits);
-    attention_decode_kernel<D><<<grid, kThreads, decode_smem<D>(), stream>>>(
-        (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
-        scale * kLog2e, window, err);
+    thn_launch(attention_decode_kernel<D>, grid, kThreads, decode_smem<D>(), stream, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
+        scale * kLog2e, window, counters, err);
     int status = thn_launch_status("attention_decode");
-    if (status != THN_OK || n_splits == 1) return status;
-    attention_merge_kernel<<<n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml,
+    if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
+    thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
                                                                             n_splits, D);
     return thn_launch_status("attention_merge");
 }
@@ -514,12 +575,23 @@ THN_API long long thn_attention_decode_scratch_floats(int n_seqs, int n_q, int n
     return (long long)n_seqs * n_q * n_splits * (head_dim + 2);
 }
 
+// Blocks of the decode kernel that one SM holds at a time (for choosing n_splits so that
+// the grid is one wave).
+THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
+    return head_dim == 64 ? decode_blocks_per_sm<64>() : decode_blocks_per_sm<128>();
+}
+
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
+// counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the
+// last block of each (sequence, kv head) combines the splits itself; null: a second kernel
+// combines them.
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window, float* scratch, int* err, cudaStream_t stream) {
+                                      int window, float* scratch, int* counters, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
+    THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
+                  n_splits);
     THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
                        "attention_decode: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
                        head_dim, page_size, n_q, n_kv);
@@ -529,8 +601,8 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
     if (head_dim == 64)
-        return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
-    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, err, stream);
+        return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
+    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
 }
 
 // ------------------------------------------------------------------ no device allocation
@@ -591,5 +663,5 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, err, stream);
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, err, stream);
 }

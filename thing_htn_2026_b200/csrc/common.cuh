@@ -56,6 +56,33 @@ static inline int thn_launch_status(const char* what) {
     return THN_OK;
 }
 
+// Programmatic dependent launch.  Every kernel of this library says at its start that the
+// next kernel in the stream may be scheduled (pdl_launch_dependents), and waits for the
+// kernels before it to finish (pdl_wait) before it reads anything they wrote or writes
+// anything at all.  What a kernel does between the two must depend on nothing but constant
+// data (weights): it runs while the previous kernel is still at work.  Without the launch
+// attribute both are no-ops.  Neither is a spin: the wait is the hardware's own.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_thn_pdl;   // 1: launch with programmatic stream serialization (elementwise.cu)
+
+template <typename... Params, typename... Args>
+inline void thn_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = g_thn_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads cudaGetLastError
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

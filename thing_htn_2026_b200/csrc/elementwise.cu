@@ -24,6 +24,11 @@ void thn_set_error(const char* fmt, ...) {
     va_end(args);
 }
 
+int g_thn_pdl = 1;
+
+// 0: plain launches; 1 (default): kernels may be scheduled while their predecessor drains.
+THN_API void thn_set_pdl(int enabled) { g_thn_pdl = enabled ? 1 : 0; }
+
 THN_API const char* thn_last_error() { return g_error; }
 THN_API int thn_abi_version() { return 1; }
 
@@ -32,6 +37,8 @@ THN_API int thn_abi_version() { return 1; }
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ index,
                                    int width, int n_table_rows, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int m = blockIdx.x;
     int row = index[m];
     if (row < 0 || row >= n_table_rows) {
@@ -49,11 +56,10 @@ THN_API int thn_gather_rows(void* out, const void* table, const int* index, int 
                   n_rows, width, n_table_rows);
     if (n_rows == 0) return THN_OK;
     if (dtype == THN_F32)
-        gather_rows_kernel<float><<<n_rows, 256, 0, stream>>>((float*)out, (const float*)table, index, width,
+        thn_launch(gather_rows_kernel<float>, n_rows, 256, 0, stream, (float*)out, (const float*)table, index, width,
                                                               n_table_rows, err);
     else if (dtype == THN_BF16)
-        gather_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)table, index, width, n_table_rows, err);
+        thn_launch(gather_rows_kernel<__nv_bfloat16>, n_rows, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, index, width, n_table_rows, err);
     else
         THN_CHECK_ARG(false, "gather_rows: unknown dtype %d", dtype);
     return thn_launch_status("gather_rows");
@@ -70,6 +76,8 @@ template <typename T, typename WT, bool ADD>
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ y, T* __restrict__ h,
                                                                Source<T> d, const WT* __restrict__ w, int width,
                                                                float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * width;
     float keep[kNormKeep];
@@ -117,6 +125,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_bf16_vec_kernel(__nv_bfloat16* _
                                                                 __nv_bfloat16* __restrict__ h,
                                                                 const __nv_bfloat16* __restrict__ d,
                                                                 const WT* __restrict__ w, int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * width;
     const int i0 = threadIdx.x * 8;
@@ -173,11 +183,9 @@ static bool launch_rmsnorm_vec(void* y, void* h, const void* d, const float* d_p
         return false;
     const int threads = ((width / 8 + 31) / 32) * 32;
     if (d)
-        rmsnorm_bf16_vec_kernel<WT, true><<<rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)y, (__nv_bfloat16*)h, (const __nv_bfloat16*)d, (const WT*)w, width, eps);
+        thn_launch(rmsnorm_bf16_vec_kernel<WT, true>, rows, threads, 0, stream, (__nv_bfloat16*)y, (__nv_bfloat16*)h, (const __nv_bfloat16*)d, (const WT*)w, width, eps);
     else
-        rmsnorm_bf16_vec_kernel<WT, false><<<rows, threads, 0, stream>>>(
-            (__nv_bfloat16*)y, (__nv_bfloat16*)h, nullptr, (const WT*)w, width, eps);
+        thn_launch(rmsnorm_bf16_vec_kernel<WT, false>, rows, threads, 0, stream, (__nv_bfloat16*)y, (__nv_bfloat16*)h, nullptr, (const WT*)w, width, eps);
     return true;
 }
 
@@ -185,9 +193,9 @@ template <typename T, typename WT>
 static void launch_rmsnorm(void* y, void* h, Source<T> d, bool add, const void* w, int rows, int width, float eps,
                            cudaStream_t stream) {
     if (add)
-        rmsnorm_kernel<T, WT, true><<<rows, kNormThreads, 0, stream>>>((T*)y, (T*)h, d, (const WT*)w, width, eps);
+        thn_launch(rmsnorm_kernel<T, WT, true>, rows, kNormThreads, 0, stream, (T*)y, (T*)h, d, (const WT*)w, width, eps);
     else
-        rmsnorm_kernel<T, WT, false><<<rows, kNormThreads, 0, stream>>>((T*)y, (T*)h, d, (const WT*)w, width, eps);
+        thn_launch(rmsnorm_kernel<T, WT, false>, rows, kNormThreads, 0, stream, (T*)y, (T*)h, d, (const WT*)w, width, eps);
 }
 
 // y = RMSNorm(h).  With d (a tensor of h's type) or d_parts (n_parts float32 partials, each
@@ -225,6 +233,8 @@ THN_API int thn_rmsnorm(void* y, void* h, const void* d, const float* d_parts, i
 // out[m, i] = rnd(rnd(g / (1 + exp(-g))) * u), g = gu[m, i], u = gu[m, inter + i].
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, Source<T> gu, long long total, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
         const long long m = e / inter;
@@ -239,6 +249,8 @@ __global__ void swiglu_kernel(T* __restrict__ out, Source<T> gu, long long total
 // bfloat16 tensor input with inter % 8 == 0: eight values per thread, 16-byte accesses.
 __global__ void swiglu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu,
                                        long long total_vecs, int inter_vecs) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total_vecs; e += stride) {
         const long long m = e / inter_vecs;
@@ -273,16 +285,13 @@ THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_p
     if (dtype == THN_BF16 && gu && inter % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
         const long long vecs = total / 8;
         const long long want_vec = (vecs + threads - 1) / threads;
-        swiglu_bf16_vec_kernel<<<(unsigned)(want_vec < 148 * 32 ? want_vec : 148 * 32), threads, 0, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, vecs, inter / 8);
+        thn_launch(swiglu_bf16_vec_kernel, (unsigned)(want_vec < 148 * 32 ? want_vec : 148 * 32), threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, vecs, inter / 8);
         return thn_launch_status("swiglu");
     }
     if (dtype == THN_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>(
-            (float*)out, Source<float>{(const float*)gu, gu_parts, n_parts, stride}, total, inter);
+        thn_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (float*)out, Source<float>{(const float*)gu, gu_parts, n_parts, stride}, total, inter);
     else if (dtype == THN_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-            (__nv_bfloat16*)out, Source<__nv_bfloat16>{(const __nv_bfloat16*)gu, gu_parts, n_parts, stride}, total,
+        thn_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out, Source<__nv_bfloat16>{(const __nv_bfloat16*)gu, gu_parts, n_parts, stride}, total,
             inter);
     else
         THN_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
@@ -293,6 +302,8 @@ THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_p
 
 template <typename T>
 __global__ void resolve_kernel(T* __restrict__ out, Source<T> src, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride)
         out[e] = from_f32<T>(src.load(e));
@@ -306,11 +317,10 @@ THN_API int thn_resolve_parts(void* out, const float* parts, int n_parts, long l
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (dtype == THN_F32)
-        resolve_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, Source<float>{nullptr, parts, n_parts, total},
+        thn_launch(resolve_kernel<float>, blocks, 256, 0, stream, (float*)out, Source<float>{nullptr, parts, n_parts, total},
                                                           total);
     else if (dtype == THN_BF16)
-        resolve_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
-            (__nv_bfloat16*)out, Source<__nv_bfloat16>{nullptr, parts, n_parts, total}, total);
+        thn_launch(resolve_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, Source<__nv_bfloat16>{nullptr, parts, n_parts, total}, total);
     else
         THN_CHECK_ARG(false, "resolve_parts: unknown dtype %d", dtype);
     return thn_launch_status("resolve_parts");
@@ -323,6 +333,8 @@ THN_API int thn_resolve_parts(void* out, const float* parts, int n_parts, long l
 __global__ void step_rows_kernel(int* __restrict__ row_slot, int* __restrict__ row_pos,
                                  const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                                  const int* __restrict__ seq_lens, int n_seqs) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     if (b >= n_seqs) return;
     const int r0 = cu_seqlens[b], r1 = cu_seqlens[b + 1];
@@ -338,13 +350,15 @@ THN_API int thn_step_rows(int* row_slot, int* row_pos, const int* cu_seqlens, co
                           int n_seqs, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0, "step_rows: bad batch %d", n_seqs);
     if (n_seqs == 0) return THN_OK;
-    step_rows_kernel<<<n_seqs, 128, 0, stream>>>(row_slot, row_pos, cu_seqlens, slots, seq_lens, n_seqs);
+    thn_launch(step_rows_kernel, n_seqs, 128, 0, stream, row_slot, row_pos, cu_seqlens, slots, seq_lens, n_seqs);
     return thn_launch_status("step_rows");
 }
 
 // seq_lens[slots[b]] += cu[b+1] - cu[b]: the step's tokens are now part of the sequences.
 __global__ void advance_kernel(int* __restrict__ seq_lens, const int* __restrict__ slots,
                                const int* __restrict__ cu_seqlens, int n_seqs) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < n_seqs) seq_lens[slots[b]] += cu_seqlens[b + 1] - cu_seqlens[b];
 }
@@ -352,7 +366,7 @@ __global__ void advance_kernel(int* __restrict__ seq_lens, const int* __restrict
 THN_API int thn_advance(int* seq_lens, const int* slots, const int* cu_seqlens, int n_seqs, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0, "advance: bad batch %d", n_seqs);
     if (n_seqs == 0) return THN_OK;
-    advance_kernel<<<(n_seqs + 127) / 128, 128, 0, stream>>>(seq_lens, slots, cu_seqlens, n_seqs);
+    thn_launch(advance_kernel, (n_seqs + 127) / 128, 128, 0, stream, seq_lens, slots, cu_seqlens, n_seqs);
     return thn_launch_status("advance");
 }
 
@@ -361,6 +375,8 @@ THN_API int thn_advance(int* seq_lens, const int* slots, const int* cu_seqlens, 
 // cos/sin of angle = position * inv_freq[i], all float32 (engine/engine.py:238-247).
 __global__ void rope_table_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out,
                                   const float* __restrict__ inv_freq, int first, int n_positions, int half) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= (long long)n_positions * half) return;
     const int p = (int)(e / half), i = (int)(e - (long long)p * half);
@@ -375,7 +391,7 @@ THN_API int thn_rope_table(float* cos_out, float* sin_out, const float* inv_freq
     THN_CHECK_ARG(first >= 0 && n_positions >= 0 && half > 0, "rope_table: bad sizes");
     const long long total = (long long)n_positions * half;
     if (total == 0) return THN_OK;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(cos_out, sin_out, inv_freq, first,
+    thn_launch(rope_table_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, cos_out, sin_out, inv_freq, first,
                                                                            n_positions, half);
     return thn_launch_status("rope_table");
 }
@@ -385,6 +401,8 @@ THN_API int thn_rope_table(float* cos_out, float* sin_out, const float* inv_freq
 // dst[index[i]] = value[i]: block-table cells and per-sequence counters changed by the host.
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const long long* __restrict__ index,
                                    const int* __restrict__ value, int n, long long dst_size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n && index[i] >= 0 && index[i] < dst_size) dst[index[i]] = value[i];
 }
@@ -393,13 +411,15 @@ THN_API int thn_scatter_i32(int* dst, const long long* index, const int* value, 
                             cudaStream_t stream) {
     THN_CHECK_ARG(n >= 0 && dst_size >= 0, "scatter_i32: bad sizes");
     if (n == 0) return THN_OK;
-    scatter_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, index, value, n, dst_size);
+    thn_launch(scatter_i32_kernel, (n + 127) / 128, 128, 0, stream, dst, index, value, n, dst_size);
     return thn_launch_status("scatter_i32");
 }
 
 // out[i] = src[index[i]]: the tokens that the sequences of a decode step feed next.
 __global__ void gather_i32_kernel(int* __restrict__ out, const int* __restrict__ src, const int* __restrict__ index,
                                   int n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = src[index[i]];
 }
@@ -407,6 +427,6 @@ __global__ void gather_i32_kernel(int* __restrict__ out, const int* __restrict__
 THN_API int thn_gather_i32(int* out, const int* src, const int* index, int n, cudaStream_t stream) {
     THN_CHECK_ARG(n >= 0, "gather_i32: bad size %d", n);
     if (n == 0) return THN_OK;
-    gather_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(out, src, index, n);
+    thn_launch(gather_i32_kernel, (n + 127) / 128, 128, 0, stream, out, src, index, n);
     return thn_launch_status("gather_i32");
 }

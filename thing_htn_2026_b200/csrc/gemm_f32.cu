@@ -10,6 +10,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A,
                                                        const float* __restrict__ W, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -62,6 +64,6 @@ THN_API int thn_gemm_f32(float* C, const float* A, const float* W, int M, int N,
     if (M == 0) return THN_OK;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     THN_UNSUPPORTED_IF(grid.y > 65535, "gemm_f32: %d rows exceed the grid limit", M);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(C, A, W, M, N, K);
+    thn_launch(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K);
     return thn_launch_status("gemm_f32");
 }

@@ -98,13 +98,28 @@ template <int MT, typename OutT>
 __global__ void __launch_bounds__(kWarps * 32, MT == 1 ? kMinBlocks : kMinBlocks - 1) gemm_smallm_kernel(
     OutT* __restrict__ out, float* __restrict__ slabs, int* __restrict__ counters,
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, int M, int N, int K, int chunks,
-    int span, long long total_units) {
+    int span, long long total_units, int prefetch) {
     const int lane = threadIdx.x & 31;
     const long long warp_global = (long long)blockIdx.x * kWarps + (threadIdx.x >> 5);
     long long u = warp_global * span;
     const long long u_end = min(u + span, total_units);
     const int g = lane >> 2, t = lane & 3;
     const size_t slab_stride = (size_t)M * N;
+
+    // While the kernel that produces x is still running, pull this warp's stretch of W
+    // towards L2: one 128-byte line per instruction, 16 rows x 2 lines per warp step.
+    pdl_launch_dependents();
+    for (long long pu = u; prefetch && pu < u_end;) {
+        const int tile = (int)(pu / chunks);
+        const int c0 = (int)(pu - (long long)tile * chunks);
+        const int c1 = (int)min((long long)chunks, c0 + (u_end - pu));
+        const int row = tile * 16 + (lane & 15);
+        if (row < N)
+            for (int c = c0 + (lane >> 4); c < c1; c += 2)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(w + (size_t)row * K + (size_t)c * kChunk));
+        pu += c1 - c0;
+    }
+    pdl_wait();
 
     const __nv_bfloat16* xr[MT];
 #pragma unroll
@@ -194,6 +209,11 @@ int resident_warps(int n_sms) {
 }  // namespace
 
 constexpr int kSmallMMax = 16;
+int g_thn_prefetch = 1;
+
+// 1 (default): the product prefetches its weights towards L2 before it waits for its input.
+THN_API void thn_set_weight_prefetch(int enabled) { g_thn_prefetch = enabled ? 1 : 0; }
+
 
 // 1 if thn_gemm_smallm_bf16 takes this shape.
 THN_API int thn_gemm_smallm_supported(int M, int N, int K) {
@@ -247,8 +267,8 @@ THN_API int thn_gemm_smallm_bf16(void* out, int out_dtype, float* slabs, int* co
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
 #define LAUNCH(MT, OutT)                                                                                      \
-    gemm_smallm_kernel<MT, OutT><<<blocks, kWarps * 32, 0, stream>>>((OutT*)out, slabs, counters, xp, wp, M, \
-                                                                    N, K, chunks, span, units)
+    thn_launch(gemm_smallm_kernel<MT, OutT>, blocks, kWarps * 32, 0, stream, (OutT*)out, slabs, counters, xp, wp, M, \
+                                                                    N, K, chunks, span, units, g_thn_prefetch)
     if (M <= 8 && out_dtype == THN_BF16) LAUNCH(1, __nv_bfloat16);
     else if (M <= 8) LAUNCH(1, float);
     else if (out_dtype == THN_BF16) LAUNCH(2, __nv_bfloat16);

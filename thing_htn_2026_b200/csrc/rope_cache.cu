@@ -16,6 +16,8 @@ __global__ void qk_norm_rope_cache_kernel(
     float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int table_len, int rotary_dim,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_rows, int n_q, int write_cache,
     int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp_in_block = threadIdx.x >> 5;
     const int n_heads_total = n_q + 2 * kv.n_kv;
@@ -92,6 +94,8 @@ __global__ void qk_norm_rope_cache_bf16_kernel(
     const WT* __restrict__ k_gain, float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
     int table_len, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_rows, int n_q,
     int write_cache, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int E = D / 64, kHalf = D / 2;
     const int lane = threadIdx.x & 31;
     const int n_heads_total = n_q + 2 * kv.n_kv;
@@ -182,7 +186,7 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
     if (dtype == THN_BF16 && qkv && q_gain && cos_tab && rotary_dim == head_dim &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
 #define FAST(WT, D)                                                                                                 \
-    qk_norm_rope_cache_bf16_kernel<WT, D><<<blocks, warps * 32, 0, stream>>>(                                        \
+    thn_launch(qk_norm_rope_cache_bf16_kernel<WT, D>, blocks, warps * 32, 0, stream, \
         (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, (const WT*)q_gain, (const WT*)k_gain, eps, cos_tab,       \
         sin_tab, table_len, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)
         bool done = true;
@@ -197,7 +201,7 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
         if (done) return thn_launch_status("qk_norm_rope_cache");
     }
 #define LAUNCH(T, WT)                                                                                              \
-    qk_norm_rope_cache_kernel<T, WT><<<blocks, warps * 32, smem, stream>>>(                                        \
+    thn_launch(qk_norm_rope_cache_kernel<T, WT>, blocks, warps * 32, smem, stream, \
         (T*)q_out, Source<T>{(const T*)qkv, qkv_parts, qkv_n_parts, part_stride}, (const WT*)q_gain,               \
         (const WT*)k_gain, eps, cos_tab, sin_tab, table_len,                                                       \
         rotary_dim, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)

@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(1024) choose_kernel(int* __restrict__ out, con
                                                       const int* __restrict__ stream_id, int* __restrict__ step,
                                                       const int* __restrict__ slots, int* __restrict__ last_token,
                                                       int bump_step) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ Best partial[32];
     const int row = blockIdx.x;
     const int who = slots ? slots[row] : row;  // index of this row's per-sequence values
@@ -111,7 +113,7 @@ THN_API int thn_choose_tokens(int* out, const float* logits, int rows, int vocab
                   "choose_tokens: sampling needs seed, stream and step arrays");
     if (rows == 0) return THN_OK;
     const int threads = vocab >= 4096 ? 1024 : 256;
-    choose_kernel<<<rows, threads, 0, stream>>>(out, logits, vocab, row_stride, temperature, seed, stream_id, step,
+    thn_launch(choose_kernel, rows, threads, 0, stream, out, logits, vocab, row_stride, temperature, seed, stream_id, step,
                                                 slots, last_token, bump_step);
     return thn_launch_status("choose_tokens");
 }

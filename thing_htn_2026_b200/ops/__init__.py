@@ -61,7 +61,8 @@ _SIGNATURES = {
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "thn_attention_decode_blocks_per_sm": [c_int],
 }
 
 _lib = None
@@ -75,6 +76,12 @@ def lib():
             fn = getattr(loaded, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        loaded.thn_set_pdl.argtypes = [c_int]
+        loaded.thn_set_pdl.restype = None
+        loaded.thn_set_pdl(0 if os.environ.get("THN_PDL", "1").strip().lower() in ("0", "false", "no", "off") else 1)
+        loaded.thn_set_weight_prefetch.argtypes = [c_int]
+        loaded.thn_set_weight_prefetch.restype = None
+        loaded.thn_set_weight_prefetch(0 if os.environ.get("THN_PREFETCH", "1").strip() in ("0", "false", "off") else 1)
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         loaded.thn_attention_decode_scratch_floats.restype = c_longlong
         _lib = loaded
@@ -318,7 +325,7 @@ def _smallm_counter_buffer(n_tiles: int, device) -> torch.Tensor:
     index = torch.device(device).index or 0
     have = _smallm_counters.get(index)
     if have is None or have.numel() < n_tiles:
-        have = torch.zeros(max(n_tiles, 16384), dtype=torch.int32, device=device)
+        have = torch.zeros(max(n_tiles, 1 << 20), dtype=torch.int32, device=device)   # never regrown in practice: graphs keep its address
         _smallm_counters[index] = have
     return have
 
@@ -445,32 +452,33 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int
     return out
 
 
-def decode_splits(n_seqs: int, n_kv: int, device) -> int:
+def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128) -> int:
     """Splits of the key range per (sequence, kv head) so that a single-token step fills the
-    GPU about twice over.  It depends on the batch only, never on the lengths, so a captured
+    GPU with one wave of blocks.  It depends on the batch only, never on the lengths, so a captured
     step stays valid while the sequences grow."""
-    want = -(-2 * _sm_count_of(device) // max(1, n_seqs * n_kv))
-    return max(1, min(32, want))
+    capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
+    return max(1, min(16, capacity // max(1, n_seqs * n_kv)))
 
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                           window: Optional[int], err: torch.Tensor, n_splits: Optional[int] = None,
-                          scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          scratch: Optional[torch.Tensor] = None, fused_merge: bool = True) -> torch.Tensor:
     """Split-KV flash decoding: one token per sequence.  Partial results of the splits go
     through float32 scratch memory, which is allocated here unless given."""
     _need(q, "attention q", torch.bfloat16)
     n_seqs = rows.n_rows
     if n_splits is None:
-        n_splits = decode_splits(n_seqs, kv.n_kv, q.device)
+        n_splits = decode_splits(n_seqs, kv.n_kv, q.device, kv.head_dim)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     if need and scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if need and scratch.numel() < need:
         raise KernelError(f"attention_decode: scratch has {scratch.numel()} floats, {need} needed")
+    counters = _smallm_counter_buffer(n_seqs * kv.n_kv, q.device) if n_splits > 1 and fused_merge else None
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
-          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(err), _stream())
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), _ptr(err), _stream())
     return out
 
 
