@@ -44,12 +44,42 @@ def time_cold(make_call, n_variants, reps):
     return sorted(times)[len(times) // 2] * 1e3   # median per call, microseconds
 
 
+def prefill_products(args):
+    """The tcgen05 product against the vendor library at prompt sizes; the fused gate/up +
+    SwiGLU against the library product followed by the SwiGLU kernel."""
+    from thing_htn_2026_b200 import ops
+    dev = "cuda:0"
+    m = args.prefill_rows
+    shapes = {"qkv": ((NQ + 2 * NKV) * D, H), "o": (H, NQ * D), "gate_up": (2 * I, H), "down": (H, I)}
+    err = ops.new_error_word(dev)
+    for name, (n, k) in shapes.items():
+        copies = max(2, int(2 * L2_BYTES / (n * k * 2)) + 1)
+        weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        flops = 2.0 * m * n * k
+        own = time_cold(lambda i: ops.linear_tcgen05(x, weights[i], err), copies, args.reps)
+        lib_us = time_cold(lambda i: torch.nn.functional.linear(x, weights[i]), copies, args.reps)
+        entry = {"own_us": own, "own_tflops": flops / own / 1e6, "library_us": lib_us,
+                 "library_tflops": flops / lib_us / 1e6}
+        if name == "gate_up":
+            fused = time_cold(lambda i: ops.linear_tcgen05(x, weights[i], err, swiglu=True), copies, args.reps)
+            both = time_cold(lambda i: ops.swiglu(torch.nn.functional.linear(x, weights[i])), copies, args.reps)
+            entry.update({"own_fused_swiglu_us": fused, "library_plus_swiglu_us": both})
+        print(f"gemm_{name}_m{m}", json.dumps({k_: round(v, 2) for k_, v in entry.items()}))
+        del weights
+    assert int(err.item()) == 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=640)
     parser.add_argument("--reps", type=int, default=20)
+    parser.add_argument("--prefill-rows", type=int, default=0,
+                        help="instead of the decode kernels, time the many-row products at this row count")
     args = parser.parse_args()
+    if args.prefill_rows:
+        return prefill_products(args)
     from thing_htn_2026_b200 import ops
     from thing_htn_2026_b200.cache import KVSpec, SequenceCache
     dev = "cuda:0"

@@ -170,9 +170,9 @@ class PagedFixture:
         if max(counts) > 1:
             r0, rn = [], []
             for start, c in zip(cu, counts):
-                for r in range(0, c, 64):
+                for r in range(0, c, o.ROW_TILE()):
                     r0.append(start + r)
-                    rn.append(min(64, c - r))
+                    rn.append(min(o.ROW_TILE(), c - r))
             rows.tile_row0 = torch.tensor(r0, dtype=torch.int32, device=DEV)
             rows.tile_rows = torch.tensor(rn, dtype=torch.int32, device=DEV)
             rows.n_tiles = len(r0)

@@ -51,8 +51,8 @@ def step_context(cache, slots, counts):
     slots_dev = torch.tensor(slots, dtype=torch.int32, device=DEV)
     rows = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts))
     if max(counts) > 1:
-        r0 = [s + r for s, c in zip(cu, counts) for r in range(0, c, 64)]
-        rn = [min(64, c - r) for c in counts for r in range(0, c, 64)]
+        r0 = [s + r for s, c in zip(cu, counts) for r in range(0, c, ops.ROW_TILE())]
+        rn = [min(ops.ROW_TILE(), c - r) for c in counts for r in range(0, c, ops.ROW_TILE())]
         rows.tile_row0 = torch.tensor(r0, dtype=torch.int32, device=DEV)
         rows.tile_rows = torch.tensor(rn, dtype=torch.int32, device=DEV)
         rows.n_tiles = len(r0)

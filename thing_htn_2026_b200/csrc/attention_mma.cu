@@ -16,7 +16,9 @@
 namespace {
 
 constexpr int kTile = 64;        // keys per tile == page size
-constexpr int kThreads = 128;    // 4 warps
+constexpr int kThreads = 128;    // 4 warps (decode)
+constexpr int kPrefillRows = 128;                          // query rows per block in the prompt kernel
+constexpr int kPrefillThreads = kPrefillRows / 16 * 32;    // one warp per 16 rows
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -49,11 +51,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // Copies a [rows_total=64][D] tile (contiguous in global memory) into padded shared rows.
-template <int D>
+template <int D, int THREADS = kThreads>
 __device__ __forceinline__ void load_tile_async(__nv_bfloat16* smem, const __nv_bfloat16* gmem) {
     constexpr int kChunksPerRow = D / 8, kPitch = D + 8;
 #pragma unroll
-    for (int c = threadIdx.x; c < kTile * kChunksPerRow; c += kThreads) {
+    for (int c = threadIdx.x; c < kTile * kChunksPerRow; c += THREADS) {
         const int row = c / kChunksPerRow, col = (c % kChunksPerRow) * 8;
         cp_async16(smem + row * kPitch + col, gmem + row * D + col);
     }
@@ -150,10 +152,10 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NK][4], RowState& st, fl
 
 // ------------------------------------------------------------------ several tokens per sequence
 
-// One block: 64 consecutive rows of one sequence (tile_row0 .. +64, clipped to the sequence)
+// One block: kPrefillRows consecutive rows of one sequence (tile_row0 .., clipped to the sequence)
 // for one query head; warp w owns rows 16w .. 16w+15.
 template <int D>
-__global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
+__global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
     __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const int* __restrict__ tile_row0,
     const int* __restrict__ tile_rows, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv,
     int n_q, float scale_log2, int window, int* __restrict__ err) {
@@ -161,8 +163,8 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
     pdl_wait();
     constexpr int kPitch = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][kPitch]
-    __nv_bfloat16* k_smem = q_smem + kTile * kPitch;                               // [2][64][kPitch]
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [rows][kPitch]
+    __nv_bfloat16* k_smem = q_smem + kPrefillRows * kPitch;                        // [2][64][kPitch]
     __nv_bfloat16* v_smem = k_smem + 2 * kTile * kPitch;                           // [2][64][kPitch]
 
     // Later tiles of a sequence see more keys and run longer: start them first, so that the
@@ -176,7 +178,7 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
     const int* pages = kv.block_table + (size_t)row_slot[row0] * kv.bt_stride;
 
     // Q tile -> shared (rows past the sequence are zero)
-    for (int c = threadIdx.x; c < kTile * (D / 8); c += kThreads) {
+    for (int c = threadIdx.x; c < kPrefillRows * (D / 8); c += kPrefillThreads) {
         const int r = c / (D / 8), col = (c % (D / 8)) * 8;
         if (r < n_rows)
             cp_async16(q_smem + r * kPitch + col, q + ((size_t)(row0 + r) * n_q + h) * D + col);
@@ -195,8 +197,8 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
             if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
         } else {
             const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
-            load_tile_async<D>(k_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 0, kvh, 0));
-            load_tile_async<D>(v_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 1, kvh, 0));
+            load_tile_async<D, kPrefillThreads>(k_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 0, kvh, 0));
+            load_tile_async<D, kPrefillThreads>(v_smem + stage * kTile * kPitch, base + kv_offset(kv, page, 1, kvh, 0));
         }
         cp_async_commit();
     };
@@ -276,7 +278,9 @@ __global__ void __launch_bounds__(kThreads) attention_prefill_kernel(
 // itself in on its (sequence, kv head), and the block that arrives last combines the
 // partials in split order (so the result does not depend on who was last) and writes the
 // output; nobody waits.  Without counters the merge kernel does it.
-template <int D>
+// STAGES: tile buffers (2 when a block has few tiles and more blocks per SM matter, 3 when
+// one block walks a whole sequence).
+template <int D, int STAGES>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int kPitch = D + 8, kStages = 2;
+    constexpr int kPitch = D + 8, kStages = STAGES;
     __shared__ int is_last;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kPitch]
@@ -328,8 +332,9 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         cp_async_commit();
     };
     issue(t_begin, 0);
+    if (kStages == 3) issue(t_begin + 1, 1);
 
-    cp_async_wait<1>();          // Q has landed
+    if (kStages == 3) cp_async_wait<2>(); else cp_async_wait<1>();          // Q has landed
     __syncthreads();
     uint32_t qf[D / 16][4];
 #pragma unroll
@@ -347,8 +352,13 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % kStages;
-        issue(t + 1, stage ^ 1);
-        cp_async_wait<1>();
+        if (kStages == 3) {
+            issue(t + 2, (stage + 2) % 3);
+            cp_async_wait<2>();
+        } else {
+            issue(t + 1, stage ^ 1);
+            cp_async_wait<1>();
+        }
         __syncthreads();
         const int key0 = t * kTile + warp * 16;
         float s[2][4];
@@ -477,8 +487,8 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     }
 }
 
-template <int D> constexpr size_t prefill_smem() { return (size_t)(kTile + 4 * kTile) * (D + 8) * 2; }
-template <int D> constexpr size_t decode_smem() { return (size_t)(16 + 4 * kTile) * (D + 8) * 2; }
+template <int D> constexpr size_t prefill_smem() { return (size_t)(kPrefillRows + 4 * kTile) * (D + 8) * 2; }
+template <int D, int STAGES> constexpr size_t decode_smem() { return (size_t)(16 + 2 * STAGES * kTile) * (D + 8) * 2; }
 
 template <int D>
 int launch_prefill(void* out, const void* q, const int* tile_row0, const int* tile_rows, int n_tiles,
@@ -496,20 +506,21 @@ int launch_prefill(void* out, const void* q, const int* tile_row0, const int* ti
         configured = true;
     }
     dim3 grid(n_tiles, n_q);
-    thn_launch(attention_prefill_kernel<D>, grid, kThreads, prefill_smem<D>(), stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
+    thn_launch(attention_prefill_kernel<D>, grid, kPrefillThreads, prefill_smem<D>(), stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
         scale * kLog2e, window, err);
     return thn_launch_status("attention_prefill");
 }
 
-template <int D>
+template <int D, int STAGES>
 int configure_decode() {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)decode_smem<D>());
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)decode_smem<D, STAGES>());
         if (e != cudaSuccess) {
-            thn_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s", decode_smem<D>(),
-                          cudaGetErrorString(e));
+            thn_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s",
+                          decode_smem<D, STAGES>(), cudaGetErrorString(e));
             return (int)e;
         }
         configured = true;
@@ -519,10 +530,10 @@ int configure_decode() {
 
 template <int D>
 int decode_blocks_per_sm() {
-    if (configure_decode<D>() != THN_OK) return 1;
+    if (configure_decode<D, 2>() != THN_OK) return 1;
     int blocks = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D>, kThreads,
-                                                                  decode_smem<D>());
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2>, kThreads,
+                                                                  decode_smem<D, 2>());
     return (e == cudaSuccess && blocks > 0) ? blocks : 1;
 }
 
@@ -530,11 +541,17 @@ template <int D>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
                   cudaStream_t stream) {
-    int configured = configure_decode<D>();
+    int configured = n_splits == 1 ? configure_decode<D, 3>() : configure_decode<D, 2>();
     if (configured != THN_OK) return configured;
     dim3 grid(n_seqs, kv.n_kv, n_splits);
-    thn_launch(attention_decode_kernel<D>, grid, kThreads, decode_smem<D>(), stream, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
-        scale * kLog2e, window, counters, err);
+    if (n_splits == 1)
+        thn_launch(attention_decode_kernel<D, 3>, grid, kThreads, decode_smem<D, 3>(), stream, (__nv_bfloat16*)out,
+                   part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits, scale * kLog2e,
+                   window, counters, err);
+    else
+        thn_launch(attention_decode_kernel<D, 2>, grid, kThreads, decode_smem<D, 2>(), stream, (__nv_bfloat16*)out,
+                   part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits, scale * kLog2e,
+                   window, counters, err);
     int status = thn_launch_status("attention_decode");
     if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
     thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
@@ -550,8 +567,11 @@ THN_API int thn_attention_mma_supported(int head_dim, int page_size, int n_q, in
            n_q / n_kv <= 16;
 }
 
+// Rows of a row tile of the prompt kernel (see thn_attention_prefill_bf16).
+THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }
+
 // Rows of a step that brings one or more tokens per sequence.  tile_row0[i] is the first
-// packed row of tile i, tile_rows[i] (1..64) the number of its rows; the rows of a tile are
+// packed row of tile i, tile_rows[i] (1..thn_attention_prefill_tile_rows()) the number of its rows; the rows of a tile are
 // consecutive tokens of one sequence.  q, out [rows, n_q * head_dim] bfloat16.
 THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile_row0, const int* tile_rows,
                                        int n_tiles, const int* row_slot, const int* row_pos, const void* kv_base,

@@ -63,10 +63,11 @@ class StepRunner:
         tile_row0: List[int] = []
         tile_rows: List[int] = []
         if max(counts) > 1:
+            size = ops.ROW_TILE()
             for start, c in zip(cu, counts):
-                for r in range(0, c, 64):
+                for r in range(0, c, size):
                     tile_row0.append(start + r)
-                    tile_rows.append(min(64, c - r))
+                    tile_rows.append(min(size, c - r))
 
         parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows, tile_row0, tile_rows]
         packed = torch.tensor([x for part in parts for x in part], dtype=torch.int32).to(self.device)

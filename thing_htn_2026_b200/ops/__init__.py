@@ -41,6 +41,8 @@ _SIGNATURES = {
     "thn_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "thn_resolve_parts": [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p],
     "thn_gemm_smallm_supported": [c_int, c_int, c_int],
+    "thn_gemm_tcgen05_supported": [c_int, c_int, c_int],
+    "thn_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_smallm_plan": [c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_gemm_smallm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_void_p],
@@ -55,7 +57,7 @@ _SIGNATURES = {
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "thn_scatter_i32": [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p],
     "thn_choose_tokens": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_void_p, c_void_p, c_int, c_void_p],
+                          c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "thn_gather_i32": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -63,6 +65,7 @@ _SIGNATURES = {
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
+    "thn_attention_prefill_tile_rows": [],
 }
 
 _lib = None
@@ -82,6 +85,8 @@ def lib():
         loaded.thn_set_weight_prefetch.argtypes = [c_int]
         loaded.thn_set_weight_prefetch.restype = None
         loaded.thn_set_weight_prefetch(0 if os.environ.get("THN_PREFETCH", "1").strip() in ("0", "false", "off") else 1)
+        loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
+        loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         loaded.thn_attention_decode_scratch_floats.restype = c_longlong
         _lib = loaded
@@ -153,7 +158,7 @@ class StepRows:
     n_rows: int
     n_seqs: int
     max_q_len: int           # longest run of rows of one sequence (host knowledge)
-    # Tiles of at most 64 consecutive rows of one sequence (first packed row, row count), for
+    # Tiles of at most ROW_TILE() consecutive rows of one sequence (first packed row, row count), for
     # kernels that work on row tiles; None when every sequence brings one row.
     tile_row0: Optional[torch.Tensor] = None
     tile_rows: Optional[torch.Tensor] = None
@@ -352,6 +357,22 @@ def linear_smallm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     return out
 
 
+def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, err: Optional[torch.Tensor] = None,
+                   swiglu: bool = False) -> torch.Tensor:
+    """The tcgen05 / TMEM / TMA product for steps with many rows: ``x [M, K] @ weight[N, K]^T``
+    in bfloat16.  With ``swiglu`` the weight is ``[2 * I, K]`` (gate rows, then up rows) and the
+    result is ``silu(gate) * up``, ``[M, I]``, in one kernel."""
+    _need(x, "linear_tcgen05 x", torch.bfloat16)
+    _need(weight, "linear_tcgen05 weight", torch.bfloat16)
+    m, k = x.shape
+    n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"linear_tcgen05: shapes x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    _call("thn_gemm_tcgen05_bf16", _ptr(out), _ptr(x), _ptr(weight), m, n, k, int(swiglu), _ptr(err), _stream())
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False):
     """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
     rows: this library's weight-streaming kernel.  bfloat16 otherwise: the vendor library's
@@ -440,6 +461,11 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
     return attention_generic(q, rows, kv, n_q, scale, window, err)
 
 
+def ROW_TILE() -> int:
+    """Rows per tile in StepRows.tile_row0 / tile_rows (what the prompt attention kernel works on)."""
+    return lib().thn_attention_prefill_tile_rows()
+
+
 def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
                            window: Optional[int], err: torch.Tensor) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence."""
@@ -505,8 +531,11 @@ def choose_tokens(logits: torch.Tensor, temperature: Optional[torch.Tensor] = No
         _need(seed, "seed", torch.int64)
         _need(stream_id, "stream", torch.int32)
         _need(step, "step", torch.int32)
+    need = lib().thn_choose_tokens_scratch_floats(rows, vocab)
+    scratch = torch.empty(need, dtype=torch.float32, device=logits.device) if need else None
     _call("thn_choose_tokens", _ptr(out), _ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature),
-          _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(slots), _ptr(last_token), int(bump_step), _stream())
+          _ptr(seed), _ptr(stream_id), _ptr(step), _ptr(slots), _ptr(last_token), int(bump_step), _ptr(scratch),
+          _stream())
     return out
 
 
@@ -520,7 +549,7 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 
 __all__ = [
-    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_smallm", "resolve", "smallm_plan", "add_rmsnorm", "advance",
-    "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_smallm", "linear_tcgen05", "resolve", "smallm_plan", "add_rmsnorm", "advance",
+    "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
