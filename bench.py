@@ -205,6 +205,7 @@ def run_ours(args):
     n_new = args.steps + 1
     list(engine.generate(e2e_prompts, 4))                   # warm: graphs for this batch exist already
     torch.cuda.synchronize()
+    uploaded_before = backend.runner.uploaded_bytes
     t0 = time.perf_counter()
     t_first = None
     count = 0
@@ -265,7 +266,10 @@ def run_ours(args):
             "peaks": peak["source"],
         },
         "e2e": {"value": e2e_decode, "unit": "tok/s", "with_prefill": e2e_total,
-                "h2d_bytes_per_step": args.batch * PROMPT * 4 / n_new, "d2h_bytes_per_step": args.batch * 4},
+                "h2d_bytes_per_step": (backend.runner.uploaded_bytes - uploaded_before) / n_new,
+                "d2h_bytes_per_step": args.batch * 4,
+                "note": "whole generate() call: prompts from pinned host memory, one token per sequence "
+                        "read back every step; value counts the decode steps, with_prefill the whole call"},
         "gpu_launches": own_per_step * args.steps,
         "own_kernels_per_step": own_per_step,
         "prefill": prefill,

@@ -121,6 +121,44 @@ def test_gemm_smallm(m, n, k):
     assert o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).dtype == torch.float32
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (100, 200, 72), (300, 1000, 136), (2048, 2560, 4096), (513, 6144, 2560),
+                                   (64, 2560, 9728)])
+def test_gemm_tcgen05(m, n, k):
+    """The tcgen05 / TMEM / TMA product against a float64 product: whole tiles, ragged edges in
+    every dimension, several tiles per block, deep and shallow reductions."""
+    o = ops()
+    x, w = rand((m, k), torch.bfloat16, 50), rand((n, k), torch.bfloat16, 51, 0.05)
+    err = o.new_error_word(DEV)
+    out = o.linear_tcgen05(x.to(DEV), w.to(DEV), err)
+    assert int(err.item()) == 0, "a pipeline wait timed out"
+    exact = x.double() @ w.double().t()
+    close(out, exact.to(torch.bfloat16), torch.bfloat16, "tcgen05 product")
+    again = o.linear_tcgen05(x.to(DEV), w.to(DEV), err)
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (300, 384, 200), (2048, 9728, 2560)])
+def test_gemm_tcgen05_fused_swiglu(m, inter, k):
+    """Gate/up product and SwiGLU in one kernel against the two plain steps.  g and u are
+    rounded to bfloat16 before the activation, as the separate product stores them; a sum in
+    another order flips such a rounding now and then, and the flip is carried through the
+    activation and the product, so the measure is bfloat16's own noise on this input (plain
+    bfloat16 against plain float32) plus one rounding step of the result."""
+    o = ops()
+    x, w = rand((m, k), torch.bfloat16, 52), rand((2 * inter, k), torch.bfloat16, 53, 0.05)
+    err = o.new_error_word(DEV)
+    out = o.linear_tcgen05(x.to(DEV), w.to(DEV), err, swiglu=True).float().cpu()
+    assert int(err.item()) == 0, "a pipeline wait timed out"
+    gu = x.float() @ w.float().t()
+    want = plain.swiglu(gu[:, :inter].to(torch.bfloat16), gu[:, inter:].to(torch.bfloat16), torch.bfloat16).float()
+    exact = plain.swiglu(gu[:, :inter], gu[:, inter:], torch.float32)
+    noise = (want - exact).abs()
+    step = torch.exp2(torch.floor(torch.log2(want.abs().clamp_min(1e-30))) - 7)
+    err_abs = (out - want).abs()
+    assert (err_abs - step).max() <= noise.max(), f"{(err_abs - step).max():.3e} beyond a rounding step"
+    assert err_abs.pow(2).mean().sqrt() <= noise.pow(2).mean().sqrt()
+
+
 def test_consumers_take_split_sums():
     """Kernels that read a product as partial sums give what they give on the summed tensor."""
     o = ops()

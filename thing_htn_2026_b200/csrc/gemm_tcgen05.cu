@@ -4,7 +4,7 @@
 // the library-free path, and the only place where the gate/up product and the SwiGLU that
 // follows it (engine/kernels/torch_ref.py:74-88) are one kernel.
 //
-// One block computes a 128 x 256 tile of the output.  Operand tiles of 64 k (128 bytes per
+// A block computes 128 x 256 tiles of the output, one after another (one block per SM).  Operand tiles of 64 k (128 bytes per
 // row) are brought to shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through
 // a ring of stages guarded by mbarriers; one thread issues tcgen05.mma (M 128, N 256, K 16,
 // four per stage) with the accumulator in 256 columns of tensor memory; tcgen05.commit
@@ -28,7 +28,7 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kThreads = 192;                         // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
-constexpr int kTmemCols = 256;
+constexpr int kTmemCols = 512;                        // two accumulators of 256 columns
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
@@ -116,23 +116,29 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
 // SWIGLU == 0: out [M, N] = x W^T, tile columns [n0, n0 + 256).
 // SWIGLU == 1: W is [2 * N, K] = cat(gate, up); out [M, N] = silu(x gate^T) * (x up^T), tile
 // columns [n0, n0 + 128); accumulator columns 0-127 are gate, 128-255 the matching up.
+//
+// A block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulator is double
+// buffered in tensor memory (2 x 256 columns): while the epilogue warps drain one tile, the
+// MMA thread is already multiplying the next one into the other half.
 template <int SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                    const __grid_constant__ CUtensorMap map_b,
                                                                    __nv_bfloat16* __restrict__ out, int M, int N,
-                                                                   int K, int* __restrict__ err) {
+                                                                   int K, int tiles_n, int n_tiles,
+                                                                   int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)kStages * kStageBytes);
     uint64_t* empty = full + kStages;
-    uint64_t* acc_done = empty + kStages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    uint64_t* acc_full = empty + kStages;      // [2] accumulator ready for the epilogue
+    uint64_t* acc_empty = acc_full + 2;        // [2] accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kTileCols = SWIGLU ? BN / 2 : BN;           // output columns of a tile
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * kTileCols;
     const int n_k = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -140,10 +146,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
-        mbar_init(acc_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(acc_full + i, 1);
+            mbar_init(acc_empty + i, 4);       // one arrival per epilogue warp
+        }
+        *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {   // one warp allocates the accumulator's columns of tensor memory
+    if (warp == 1) {   // one warp allocates both accumulators' columns of tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
                      "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -155,49 +165,69 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer
-        for (int kb = 0; kb < n_k; ++kb) {
-            const int s = kb % kStages;
-            if (!mbar_wait(empty + s, ((kb / kStages) & 1) ^ 1)) {
-                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
-                break;
-            }
-            unsigned char* a_dst = tiles + (size_t)s * kStageBytes;
-            unsigned char* b_dst = a_dst + kABytes;
-            mbar_expect_tx(full + s, kStageBytes);
-            tma_load_2d(a_dst, &map_a, full + s, kb * BK, m0);
-            if (SWIGLU) {
-                tma_load_2d(b_dst, &map_b, full + s, kb * BK, n0);                    // 128 gate rows
-                tma_load_2d(b_dst + kBBytes / 2, &map_b, full + s, kb * BK, N + n0);  // 128 up rows
-            } else {
-                tma_load_2d(b_dst, &map_b, full + s, kb * BK, n0);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !*give_up; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * kTileCols;
+            for (int kb = 0; kb < n_k; ++kb, ++it) {
+                const int s = it % kStages;
+                if (!mbar_wait(empty + s, ((it / kStages) & 1) ^ 1)) {
+                    if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                    *give_up = 1;
+                    break;
+                }
+                unsigned char* a_dst = tiles + (size_t)s * kStageBytes;
+                unsigned char* b_dst = a_dst + kABytes;
+                mbar_expect_tx(full + s, kStageBytes);
+                tma_load_2d(a_dst, &map_a, full + s, kb * BK, m0);
+                if (SWIGLU) {
+                    tma_load_2d(b_dst, &map_b, full + s, kb * BK, n0);                    // 128 gate rows
+                    tma_load_2d(b_dst + kBBytes / 2, &map_b, full + s, kb * BK, N + n0);  // 128 up rows
+                } else {
+                    tma_load_2d(b_dst, &map_b, full + s, kb * BK, n0);
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
-        bool ok = true;
-        for (int kb = 0; kb < n_k && ok; ++kb) {
-            const int s = kb % kStages;
-            ok = mbar_wait(full + s, (kb / kStages) & 1);
-            if (!ok) break;
+        int it = 0, local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !*give_up; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            bool ok = mbar_wait(acc_empty + buf, ((local >> 1) & 1) ^ 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
-            const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + kABytes);
+            const uint32_t tmem_d = tmem_base + buf * BN;
+            for (int kb = 0; kb < n_k && ok; ++kb, ++it) {
+                const int s = it % kStages;
+                ok = mbar_wait(full + s, (it / kStages) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_addr(tiles + (size_t)s * kStageBytes);
+                const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + kABytes);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K: + 2 in the address field
-                umma(tmem_base, a_desc + 2 * k, b_desc + 2 * k, (kb | k) != 0);
-            umma_commit(empty + s);                    // the stage is free when these products are done
+                for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K: + 2 in the address field
+                    umma(tmem_d, a_desc + 2 * k, b_desc + 2 * k, (kb | k) != 0);
+                umma_commit(empty + s);                    // the stage is free when these products are done
+            }
+            umma_commit(acc_full + buf);
+            if (!ok) {
+                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                *give_up = 1;
+            }
         }
-        if (!ok && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
-        umma_commit(acc_done);
     } else if (warp >= 2) {
         // ---- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 (= tile rows)
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        if (!mbar_wait(acc_done, 0)) {
-            if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
-        } else {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !*give_up; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * kTileCols;
+            const int row = m0 + quarter * 32 + lane;
+            if (!mbar_wait(acc_full + buf, (local >> 1) & 1)) {
+                if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                *give_up = 1;
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < kTileCols; c += 32) {
                 uint32_t v[32], u[32];
@@ -228,6 +258,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
                     }
                 }
             }
+            // this warp has read its quarter of the accumulator: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(acc_empty + buf)) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -306,13 +341,22 @@ THN_API int thn_gemm_tcgen05_bf16(void* out, const void* x, const void* w, int M
         return THN_BAD_ARGUMENT;
     }
     const int tile_cols = swiglu ? BN / 2 : BN;
-    dim3 grid((N + tile_cols - 1) / tile_cols, (M + BM - 1) / BM);
-    THN_UNSUPPORTED_IF(grid.y > 65535, "gemm_tcgen05: %d rows exceed the grid limit", M);
+    const int tiles_n = (N + tile_cols - 1) / tile_cols;
+    const long long n_tiles = (long long)tiles_n * ((M + BM - 1) / BM);
+    THN_UNSUPPORTED_IF(n_tiles > 0x7fffffff, "gemm_tcgen05: too many tiles");
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device);
+        if (n_sms <= 0) n_sms = 1;
+    }
+    const unsigned grid = (unsigned)(n_tiles < n_sms ? n_tiles : n_sms);
     if (swiglu)
         thn_launch(gemm_tcgen05_kernel<1>, grid, kThreads, kSmemBytes, stream, map_a, map_b, (__nv_bfloat16*)out, M, N,
-                   K, err);
+                   K, tiles_n, (int)n_tiles, err);
     else
         thn_launch(gemm_tcgen05_kernel<0>, grid, kThreads, kSmemBytes, stream, map_a, map_b, (__nv_bfloat16*)out, M, N,
-                   K, err);
+                   K, tiles_n, (int)n_tiles, err);
     return thn_launch_status("gemm_tcgen05");
 }

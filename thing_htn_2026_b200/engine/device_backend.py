@@ -117,7 +117,7 @@ class DeviceBackend:
     def launch_prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> _Handle:
         entries = [StepEntry(slot, prompt, (len(prompt) - 1,)) for slot, prompt in zip(slots, prompts)]
         logits = self.runner.step(entries, check=False)
-        slots_dev = torch.tensor(list(slots), dtype=torch.int32).to(self.device)
+        slots_dev = self.runner._upload(list(slots))
         out = torch.empty(len(slots), dtype=torch.int32, device=self.device)
         self._choose(logits, slots_dev, out)
         return self._send(out, len(slots))

@@ -38,6 +38,27 @@ class StepRunner:
         self.device = model.device
         self.err = ops.new_error_word(self.device)
         model.ensure_positions(cache.max_pages_per_seq * cache.page_size)
+        # Host-to-device uploads go through a small ring of pinned buffers; a buffer is reused
+        # only after the copy that read it has finished.
+        self._staging = [[None, None] for _ in range(4)]     # [pinned int32 tensor, event]
+        self._staging_next = 0
+        self.uploaded_bytes = 0
+
+    def _upload(self, values: List[int]) -> torch.Tensor:
+        """One asynchronous copy of ``values`` (int32) from pinned host memory."""
+        slot = self._staging[self._staging_next]
+        self._staging_next = (self._staging_next + 1) % len(self._staging)
+        n = len(values)
+        if slot[0] is None or slot[0].numel() < n:
+            slot[0] = torch.empty(max(1024, 2 * n), dtype=torch.int32, pin_memory=True)
+            slot[1] = torch.cuda.Event()
+        else:
+            slot[1].synchronize()
+        slot[0].numpy()[:n] = values          # through numpy: the buffer may have been made in inference mode
+        device = slot[0][:n].to(self.device, non_blocking=True)
+        slot[1].record()
+        self.uploaded_bytes += 4 * n
+        return device
 
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
         """Runs the entries' tokens; returns float32 logits ``[wanted, vocab]`` in the order
@@ -70,7 +91,7 @@ class StepRunner:
                     tile_rows.append(min(size, c - r))
 
         parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows, tile_row0, tile_rows]
-        packed = torch.tensor([x for part in parts for x in part], dtype=torch.int32).to(self.device)
+        packed = self._upload([x for part in parts for x in part])
         views, at = [], 0
         for part in parts:
             views.append(packed[at:at + len(part)])
