@@ -265,10 +265,12 @@ def attention_case(kernel, dtype, n_q, n_kv, D, lengths, new_counts, window, see
         got = o.attention_generic(q, rows, fix.kv, n_q, scale, window, err)
     elif kernel == "prefill":
         got = o.attention_prefill_bf16(q, rows, fix.kv, n_q, scale, window, err)
+    elif kernel == "tcgen05":
+        got = o.attention_prefill_tcgen05(q, rows, fix.kv, n_q, scale, window, err)
     elif kernel.startswith("decode"):
         got = o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, window, err,
                                       n_splits=int(kernel[6:]) if len(kernel) > 6 else None)
-    assert int(err.item()) == 0
+    assert int(err.item()) == 0, f"device error word {int(err.item())}"
     want = torch.cat([plain.attention(qs, ks, vs, scale, window, dtype)[-c:]
                       for qs, ks, vs, c in zip(q_all, k_all, v_all, new_counts)])
     return got.cpu(), want
@@ -294,6 +296,16 @@ def test_attention_prefill_tensor_cores(n_q, n_kv, D, window):
     close(got, want, dtype, "prefill attention, whole prompts")
     got, want = attention_case("prefill", dtype, n_q, n_kv, D, [300, 90, 129], [170, 64, 1], window)
     close(got, want, dtype, "prefill attention, continued prompts")
+
+
+@pytest.mark.parametrize("n_q,n_kv,window", [(2, 1, None), (8, 2, None), (6, 3, 70), (3, 1, 24), (5, 5, 200)])
+def test_attention_prefill_tcgen05(n_q, n_kv, window):
+    """The tcgen05 prompt kernel: whole prompts (one row to several tiles) and continued ones."""
+    dtype, D = torch.bfloat16, 128
+    got, want = attention_case("tcgen05", dtype, n_q, n_kv, D, [70, 5, 131, 64, 1, 257], [70, 5, 131, 64, 1, 257], window)
+    close(got, want, dtype, "tcgen05 attention, whole prompts")
+    got, want = attention_case("tcgen05", dtype, n_q, n_kv, D, [300, 90, 129, 500], [170, 64, 1, 300], window)
+    close(got, want, dtype, "tcgen05 attention, continued prompts")
 
 
 @pytest.mark.parametrize("splits", ["", "1", "3", "8"])

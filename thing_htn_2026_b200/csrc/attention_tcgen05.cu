@@ -1,0 +1,463 @@
+// Causal grouped-query flash attention for prompts on Blackwell's fifth-generation tensor
+// cores, over the paged cache (bfloat16, head size 128, pages of 64 keys).  The reference
+// calls a library's flash attention here (engine/engine.py:1123-1131, :1165-1179); the
+// arithmetic is engine/kernels/torch_ref.py:168-227: scores and softmax in float32, the
+// un-normalised probabilities rounded to bfloat16 before they multiply V, one division by
+// the float32 row sum at the end.
+//
+// One block: 128 consecutive rows of one sequence, one query head.  Row r of the tile is
+// lane r of tensor memory and is owned by one thread of the four softmax warps, so a row's
+// maximum and sum need no shuffles.  Per tile of 64 keys (one page):
+//   S = Q K^T      tcgen05.mma, M 128, N 64, K 16 x 8; Q and K tiles in shared memory (TMA,
+//                  128-byte swizzle, K-major), S in 64 columns of tensor memory;
+//   softmax        each thread reads its row of S (tcgen05.ld), masks, takes the running
+//                  maximum, rescales the output accumulator in tensor memory when the
+//                  maximum moved, writes exp2 of its row as bfloat16 to shared memory (P);
+//   O += P V       tcgen05.mma, M 128, N 128, K 16 x 4; P K-major from shared memory, the V
+//                  page as it lies in the cache ([key][d]: the N index contiguous, an
+//                  MN-major operand), O in 128 columns of tensor memory.
+// K and V pages come through a two-stage ring filled by TMA from a tensor map over the
+// cache entry.  The steps of one tile run one after another; two blocks per SM overlap.
+//
+// Every wait on an mbarrier is bounded (see gemm_tcgen05.cu); a waiter that gives up sets
+// THN_ERR_WAIT_TIMEOUT and all roles leave through the common exit.
+#include <cuda.h>
+#include <math.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRows = 128, kKeys = 64, D = 128;
+constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: softmax
+constexpr int kStages = 2;
+constexpr int kTmemCols = 256;                    // S: columns 0-63, O: columns 64-191
+constexpr int kColS = 0, kColO = 64;
+constexpr uint32_t kQBytes = kRows * D * 2;       // 32 KB: two [128 x 64] swizzled blocks
+constexpr uint32_t kKBytes = kKeys * D * 2;       // 16 KB: two [64 x 64] blocks
+constexpr uint32_t kVBytes = kKeys * D * 2;       // 16 KB: two [64 keys x 64 d] blocks
+constexpr uint32_t kPBytes = kRows * kKeys * 2;   // 16 KB: one [128 x 64] block
+constexpr uint32_t kStageBytes = kKBytes + kVBytes;
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 1024 + 256;
+constexpr unsigned long long kWaitLimitNs = 20ull * 1000 * 1000;   // a wait gives up after 20 ms
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    unsigned long long start = 0;
+    for (int spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 63) == 63) {                  // look at the clock now and then
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > kWaitLimitNs) return false;
+            __nanosleep(64);
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptors, 128-byte swizzle, version 1 (see gemm_tcgen05.cu).
+// K-major (rows of 64 k = 128 bytes; 8 rows = 1024 bytes apart): Q, K and P.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major (rows of 64 n = 128 bytes, one row per k; 8 k = 1024 bytes apart; the next 64 n
+// lie `next_n_block` bytes further): the V page, n = d, k = key.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t next_n_block) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(next_n_block >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptors, kind::f16, float32 accumulator, bfloat16 operands.
+constexpr uint32_t instr_desc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+constexpr uint32_t kDescS = instr_desc(kRows, kKeys, 0);   // S = Q K^T: both K-major
+constexpr uint32_t kDescO = instr_desc(kRows, D, 1);       // O += P V: V MN-major
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&r)[32]) {
+    uint32_t v[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(v[i]);
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const float (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])),
+          "r"(__float_as_uint(r[3])), "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])),
+          "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])), "r"(__float_as_uint(r[8])),
+          "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+          "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])),
+          "r"(__float_as_uint(r[15])), "r"(__float_as_uint(r[16])), "r"(__float_as_uint(r[17])),
+          "r"(__float_as_uint(r[18])), "r"(__float_as_uint(r[19])), "r"(__float_as_uint(r[20])),
+          "r"(__float_as_uint(r[21])), "r"(__float_as_uint(r[22])), "r"(__float_as_uint(r[23])),
+          "r"(__float_as_uint(r[24])), "r"(__float_as_uint(r[25])), "r"(__float_as_uint(r[26])),
+          "r"(__float_as_uint(r[27])), "r"(__float_as_uint(r[28])), "r"(__float_as_uint(r[29])),
+          "r"(__float_as_uint(r[30])), "r"(__float_as_uint(r[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// map_q: q as [rows, n_q * 128], boxes of 64 x 128 rows.  map_kv: the cache entry as
+// [pages * 2 * n_kv * 64, 128], boxes of 64 x 64 rows (one half of one head's page).
+__global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+    __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
+    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int* __restrict__ err, int debug_stop) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* q_smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* kv_smem = q_smem + kQBytes;                         // [stage][K 16 KB | V 16 KB]
+    unsigned char* p_smem = kv_smem + kStages * kStageBytes;
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(p_smem + kPBytes);
+    uint64_t* kv_full = q_full + 1;              // [kStages]
+    uint64_t* kv_empty = kv_full + kStages;      // [kStages]
+    uint64_t* s_full = kv_empty + kStages;       // S = Q K^T of this tile is in tensor memory
+    uint64_t* p_ready = s_full + 1;              // P of this tile is in shared memory (4 arrivals)
+    uint64_t* o_full = p_ready + 1;              // O += P V of this tile is done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;     // long tiles first
+    const int row0 = tile_row0[tile], n_rows = tile_rows[tile];
+    const int kvh = h / (n_q / n_kv);
+    const int pos0 = row_pos[row0], pos_last = pos0 + n_rows - 1;
+    int first_key = 0;
+    if (window > 0 && pos0 - window + 1 > 0) first_key = pos0 - window + 1;
+    const int t_first = first_key / kKeys, t_last = pos_last / kKeys;
+    const int* pages = block_table + (size_t)row_slot[row0] * bt_stride;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(kv_full + s, 1);
+            mbar_init(kv_empty + s, 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(p_ready, 4);
+        mbar_init(o_full, 1);
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
+                     "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: Q once, then one K page and one V page per tile
+        mbar_expect_tx(q_full, kQBytes);
+        tma_load_2d(q_smem, &map_q, q_full, h * D, row0);
+        tma_load_2d(q_smem + kQBytes / 2, &map_q, q_full, h * D + 64, row0);
+        int it = 0;
+        for (int t = t_first; t <= t_last && !*give_up && debug_stop != 1; ++t, ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait(kv_empty + s, ((it / kStages) & 1) ^ 1)) {
+                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT | 64);
+                *give_up = 1;
+                break;
+            }
+            const int page = pages[t];
+            if (page < 0) {
+                if (err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+                *give_up = 1;
+                break;
+            }
+            unsigned char* k_dst = kv_smem + (size_t)s * kStageBytes;
+            unsigned char* v_dst = k_dst + kKBytes;
+            const int k_row = ((page * 2 + 0) * n_kv + kvh) * kKeys, v_row = ((page * 2 + 1) * n_kv + kvh) * kKeys;
+            mbar_expect_tx(kv_full + s, kStageBytes);
+            tma_load_2d(k_dst, &map_kv, kv_full + s, 0, k_row);
+            tma_load_2d(k_dst + kKBytes / 2, &map_kv, kv_full + s, 64, k_row);
+            tma_load_2d(v_dst, &map_kv, kv_full + s, 0, v_row);
+            tma_load_2d(v_dst + kVBytes / 2, &map_kv, kv_full + s, 64, v_row);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        bool ok = mbar_wait(q_full, 0);
+        if (!ok && err) atomicOr(err, 16);
+        int it = 0;
+        for (int t = t_first; t <= t_last && ok && !*give_up && debug_stop != 1; ++t, ++it) {
+            const int s = it % kStages;
+            ok = mbar_wait(kv_full + s, (it / kStages) & 1);
+            if (!ok) { if (err) atomicOr(err, 32); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t q_addr = smem_addr(q_smem), k_addr = smem_addr(kv_smem + (size_t)s * kStageBytes);
+            const uint32_t v_addr = k_addr + kKBytes;
+            // S = Q K^T: eight k steps of 16 d; d 0-63 in the first swizzled block, 64-127 in the second
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint64_t a = desc_k_major(q_addr + (k / 4) * (kQBytes / 2) + (k % 4) * 32);
+                const uint64_t b = desc_k_major(k_addr + (k / 4) * (kKBytes / 2) + (k % 4) * 32);
+                umma(tmem_base + kColS, a, b, kDescS, k != 0);
+            }
+            umma_commit(s_full);
+            if (debug_stop == 2) break;
+            ok = mbar_wait(p_ready, it & 1);      // P is in shared memory; O has been rescaled
+            if (!ok) { if (err) atomicOr(err, 256); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // O += P V: four k steps of 16 keys; V rows are keys, 16 keys = 2048 bytes further
+#pragma unroll
+            for (int k = 0; k < kKeys / 16; ++k) {
+                const uint64_t a = desc_k_major(smem_addr(p_smem) + k * 32);
+                const uint64_t b = desc_mn_major(v_addr + k * 2048, kVBytes / 2);
+                umma(tmem_base + kColO, a, b, kDescO, (it | k) != 0);
+            }
+            if (debug_stop == 3) break;
+            umma_commit(kv_empty + s);            // the stage is free when these products are done
+            umma_commit(o_full);
+        }
+        if (!ok) {
+            if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+            *give_up = 1;
+        }
+    } else if (warp >= 2) {
+        // ---- softmax: thread = row.  Warp w owns tensor-memory lanes 32 * (w % 4) .. + 31.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                   // row of the tile
+        const int pos = pos0 + r;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float run_max = -INFINITY, run_sum = 0.f;
+        bool ok = true;
+        int it = 0;
+        for (int t = t_first; t <= t_last && !*give_up && debug_stop != 1; ++t, ++it) {
+            ok = mbar_wait(s_full, it & 1);
+            if (!ok) { if (lane == 0 && err) atomicOr(err, 128); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float s[64];
+            {
+                float part[32];
+                tmem_load_32(lane_base + kColS, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[i] = part[i];
+                tmem_load_32(lane_base + kColS + 32, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
+            }
+            if (debug_stop == 2) break;
+            const int key0 = t * kKeys;
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const int key = key0 + i;
+                const bool visible = key <= pos && (window <= 0 || key > pos - window);
+                s[i] = visible ? s[i] * scale_log2 : -INFINITY;
+                tile_max = fmaxf(tile_max, s[i]);
+            }
+            const float new_max = fmaxf(run_max, tile_max);
+            const float base = new_max == -INFINITY ? 0.f : new_max;      // no visible key yet
+            const float corr = exp2f(run_max - base);                      // 0 on the first tile
+            run_max = new_max;
+            float sum = 0.f;
+            // P, rounded to bfloat16, into the K-major swizzled tile: row r, 16-byte chunk c at
+            // chunk (c ^ (r % 8)) of the row's 128 bytes.
+            unsigned char* p_row = p_smem + (size_t)r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint4 packed;
+                __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float p = exp2f(s[c * 8 + e] - base);
+                    sum += p;
+                    pb[e] = __float2bfloat16_rn(p);
+                }
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+            }
+            run_sum = run_sum * corr + sum;
+            if (it > 0) {
+                // the previous O += P V must be complete before O is rescaled
+                ok = mbar_wait(o_full, (it - 1) & 1);
+                if (!ok) { if (lane == 0 && err) atomicOr(err, 512); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // tcgen05.ld/st are warp-wide: the whole warp rescales if any of its rows must
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        float o[32];
+                        tmem_load_32(lane_base + kColO + c, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= corr;
+                        tmem_store_32(lane_base + kColO + c, o);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+            if (debug_stop == 3) break;
+        }
+        if (ok && !*give_up && it > 0 && debug_stop == 0) {
+            ok = mbar_wait(o_full, (it - 1) & 1);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float inv = 1.0f / run_sum;
+                __nv_bfloat16* dst = out + ((size_t)(row0 + r) * n_q + h) * D;
+#pragma unroll 1
+                for (int c = 0; c < D; c += 32) {
+                    float o[32];
+                    tmem_load_32(lane_base + kColO + c, o);
+                    if (r < n_rows) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 packed;
+                            __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) pb[e] = __float2bfloat16_rn(o[j + e] * inv);
+                            *reinterpret_cast<uint4*>(dst + c + j) = packed;
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+            *give_up = 1;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bfloat16 matrix with boxes of 64 columns x box_rows rows.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// 1 if thn_attention_prefill_tcgen05 takes this shape.
+THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q, int n_kv) {
+    return head_dim == D && page_size == kKeys && n_kv > 0 && n_q % n_kv == 0;
+}
+
+// Same contract as thn_attention_prefill_bf16 with row tiles of 128 rows (tile_rows 1..128);
+// n_rows_total is the number of packed rows of q and out, n_pages the pages of the cache entry.
+THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* tile_row0, const int* tile_rows,
+                                          int n_tiles, int n_rows_total, const int* row_slot, const int* row_pos,
+                                          const void* kv_base, long long n_pages, const int* block_table,
+                                          int bt_stride, int n_kv, int page_size, int head_dim, int n_q, float scale,
+                                          int window, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_tiles >= 0 && n_q > 0 && n_rows_total >= 0 && n_pages > 0, "attention_tcgen05: bad sizes");
+    THN_UNSUPPORTED_IF(!thn_attention_tcgen05_supported(head_dim, page_size, n_q, n_kv),
+                       "attention_tcgen05: head_dim %d, page %d, heads %d/%d not supported", head_dim, page_size, n_q,
+                       n_kv);
+    THN_CHECK_ARG((((uintptr_t)q | (uintptr_t)out | (uintptr_t)kv_base) & 15) == 0,
+                  "attention_tcgen05: operands must be 16-byte aligned");
+    if (n_tiles == 0) return THN_OK;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBytes);
+        if (e != cudaSuccess) {
+            thn_set_error("attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", kSmemBytes,
+                          cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    CUtensorMap map_q, map_kv;
+    if (!make_map(&map_q, q, n_rows_total, (long long)n_q * D, kRows) ||
+        !make_map(&map_kv, kv_base, n_pages * 2 * n_kv * kKeys, D, kKeys)) {
+        thn_set_error("attention_tcgen05: cuTensorMapEncodeTiled failed");
+        return THN_BAD_ARGUMENT;
+    }
+    dim3 grid(n_tiles, n_q);
+    thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
+               tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window, err,
+               getenv("THN_DEBUG_STOP") ? atoi(getenv("THN_DEBUG_STOP")) : 0);
+    return thn_launch_status("attention_tcgen05");
+}

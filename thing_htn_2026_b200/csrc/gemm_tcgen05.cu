@@ -16,7 +16,7 @@
 // concatenated weight); the epilogue stores rnd(rnd(silu(g)) * u), where g and u are first
 // rounded to bfloat16 as the separate product would have stored them.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter sets
+// Every wait on an mbarrier is bounded: after kWaitLimitNs by the global timer the waiter sets
 // THN_ERR_WAIT_TIMEOUT in the caller's error word and goes on to the common exit, where
 // tensor memory is given back.  No wait depends on another block.
 #include <cuda.h>
@@ -32,7 +32,7 @@ constexpr int kTmemCols = 512;                        // two accumulators of 256
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
-constexpr int kSpinLimit = 100000;      // polls of up to 2 microseconds each: a wait gives up after ~0.2 s
+constexpr unsigned long long kWaitLimitNs = 20ull * 1000 * 1000;   // a wait gives up after 20 ms
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -45,22 +45,28 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 // Bounded wait for the phase with the given parity.  Returns false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
-    for (int spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned long long start = 0;
+    for (int spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n"
             ".reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
             "selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+        if ((spin & 63) == 63) {                  // look at the clock now and then
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > kWaitLimitNs) return false;
+            __nanosleep(64);
+        }
     }
-    return false;
 }
-
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -66,6 +66,10 @@ _SIGNATURES = {
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_prefill_tile_rows": [],
+    "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
+    "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                      c_int, c_void_p, c_void_p],
 }
 
 _lib = None
@@ -457,8 +461,26 @@ def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: floa
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err)
         if rows.tile_row0 is not None:
+            if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
+                return attention_prefill_tcgen05(q, rows, kv, n_q, scale, window, err)
             return attention_prefill_bf16(q, rows, kv, n_q, scale, window, err)
     return attention_generic(q, rows, kv, n_q, scale, window, err)
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+                              window: Optional[int], err: torch.Tensor) -> torch.Tensor:
+    """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
+    (bfloat16, head size 128)."""
+    _need(q, "attention q", torch.bfloat16)
+    out = torch.empty_like(q)
+    _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(rows.tile_row0), _ptr(rows.tile_rows),
+          rows.n_tiles, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
+          _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
+          int(window or 0), _ptr(err), _stream())
+    return out
+
+
+USE_TCGEN05_ATTENTION = os.environ.get("THN_ATTN_TCGEN05", "1").strip().lower() not in ("0", "false", "no", "off")
 
 
 def ROW_TILE() -> int:
@@ -550,6 +572,6 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_smallm", "linear_tcgen05", "resolve", "smallm_plan", "add_rmsnorm", "advance",
-    "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
+    "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
