@@ -23,7 +23,6 @@
 // THN_ERR_WAIT_TIMEOUT and all roles leave through the common exit.
 #include <cuda.h>
 #include <math.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -32,14 +31,14 @@ namespace {
 constexpr int kRows = 128, kKeys = 64, D = 128;
 constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: softmax
 constexpr int kStages = 2;
-constexpr int kTmemCols = 256;                    // S: columns 0-63, O: columns 64-191
-constexpr int kColS = 0, kColO = 64;
+constexpr int kTmemCols = 256;                    // S (two buffers): columns 0-63 and 64-127, O: columns 128-255
+constexpr int kColS = 0, kColO = 128;
 constexpr uint32_t kQBytes = kRows * D * 2;       // 32 KB: two [128 x 64] swizzled blocks
 constexpr uint32_t kKBytes = kKeys * D * 2;       // 16 KB: two [64 x 64] blocks
 constexpr uint32_t kVBytes = kKeys * D * 2;       // 16 KB: two [64 keys x 64 d] blocks
 constexpr uint32_t kPBytes = kRows * kKeys * 2;   // 16 KB: one [128 x 64] block
 constexpr uint32_t kStageBytes = kKBytes + kVBytes;
-constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 1024 + 256;
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 128;   // two blocks fit one SM
 constexpr unsigned long long kWaitLimitNs = 20ull * 1000 * 1000;   // a wait gives up after 20 ms
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -53,29 +52,34 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// Bounded wait: try_wait parks the thread in hardware for a short while instead of spinning
+// (spinning warps would take issue slots from the softmax warps); the global timer bounds
+// the whole wait.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_addr(bar);
     unsigned long long start = 0;
-    for (int spin = 0;; ++spin) {
+    for (;;) {
         uint32_t done;
         asm volatile(
             "{\n"
             ".reg .pred p;\n"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n"
             "selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if ((spin & 63) == 63) {                  // look at the clock now and then
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-            if (start == 0) start = now;
-            else if (now - start > kWaitLimitNs) return false;
-            __nanosleep(64);
-        }
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (start == 0) start = now;
+        else if (now - start > kWaitLimitNs) return false;
     }
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
@@ -160,18 +164,18 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, const int* __restrict__ block_table,
-    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int* __restrict__ err, int debug_stop) {
+    int bt_stride, int n_kv, int n_q, float scale_log2, int window, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* q_smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
+    unsigned char* q_smem = smem_raw;
     unsigned char* kv_smem = q_smem + kQBytes;                         // [stage][K 16 KB | V 16 KB]
     unsigned char* p_smem = kv_smem + kStages * kStageBytes;
     uint64_t* q_full = reinterpret_cast<uint64_t*>(p_smem + kPBytes);
     uint64_t* kv_full = q_full + 1;              // [kStages]
     uint64_t* kv_empty = kv_full + kStages;      // [kStages]
-    uint64_t* s_full = kv_empty + kStages;       // S = Q K^T of this tile is in tensor memory
-    uint64_t* p_ready = s_full + 1;              // P of this tile is in shared memory (4 arrivals)
+    uint64_t* s_full = kv_empty + kStages;       // [2] S = Q K^T of a tile is in tensor memory (two buffers)
+    uint64_t* p_ready = s_full + 2;              // P of this tile is in shared memory (4 arrivals)
     uint64_t* o_full = p_ready + 1;              // O += P V of this tile is done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -193,6 +197,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             mbar_init(kv_empty + s, 1);
         }
         mbar_init(s_full, 1);
+        mbar_init(s_full + 1, 1);
         mbar_init(p_ready, 4);
         mbar_init(o_full, 1);
         *give_up = 0;
@@ -214,10 +219,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         tma_load_2d(q_smem, &map_q, q_full, h * D, row0);
         tma_load_2d(q_smem + kQBytes / 2, &map_q, q_full, h * D + 64, row0);
         int it = 0;
-        for (int t = t_first; t <= t_last && !*give_up && debug_stop != 1; ++t, ++it) {
+        for (int t = t_first; t <= t_last && !*give_up; ++t, ++it) {
             const int s = it % kStages;
             if (!mbar_wait(kv_empty + s, ((it / kStages) & 1) ^ 1)) {
-                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT | 64);
+                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 *give_up = 1;
                 break;
             }
@@ -237,29 +242,37 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             tma_load_2d(v_dst + kVBytes / 2, &map_kv, kv_full + s, 64, v_row);
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer
+        // ---- MMA issuer.  S of tile it + 1 is multiplied while the softmax warps work on
+        // tile it; O += P V of tile it follows as soon as its P is ready.
         bool ok = mbar_wait(q_full, 0);
-        if (!ok && err) atomicOr(err, 16);
-        int it = 0;
-        for (int t = t_first; t <= t_last && ok && !*give_up && debug_stop != 1; ++t, ++it) {
+        const int n_it = t_last - t_first + 1;
+        const uint32_t q_addr = smem_addr(q_smem);
+        auto qk = [&](int it) {          // S[it & 1] = Q K(it)^T
             const int s = it % kStages;
-            ok = mbar_wait(kv_full + s, (it / kStages) & 1);
-            if (!ok) { if (err) atomicOr(err, 32); break; }
+            if (!mbar_wait(kv_full + s, (it / kStages) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t q_addr = smem_addr(q_smem), k_addr = smem_addr(kv_smem + (size_t)s * kStageBytes);
-            const uint32_t v_addr = k_addr + kKBytes;
-            // S = Q K^T: eight k steps of 16 d; d 0-63 in the first swizzled block, 64-127 in the second
+            const uint32_t k_addr = smem_addr(kv_smem + (size_t)s * kStageBytes);
+            // eight k steps of 16 d; d 0-63 in the first swizzled block, 64-127 in the second
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint64_t a = desc_k_major(q_addr + (k / 4) * (kQBytes / 2) + (k % 4) * 32);
                 const uint64_t b = desc_k_major(k_addr + (k / 4) * (kKBytes / 2) + (k % 4) * 32);
-                umma(tmem_base + kColS, a, b, kDescS, k != 0);
+                umma(tmem_base + kColS + (it & 1) * kKeys, a, b, kDescS, k != 0);
             }
-            umma_commit(s_full);
-            if (debug_stop == 2) break;
+            umma_commit(s_full + (it & 1));
+            return true;
+        };
+        if (ok && n_it > 0) ok = qk(0);
+        for (int it = 0; it < n_it && ok && !*give_up; ++it) {
+            if (it + 1 < n_it) {
+                ok = qk(it + 1);
+                if (!ok) break;
+            }
             ok = mbar_wait(p_ready, it & 1);      // P is in shared memory; O has been rescaled
-            if (!ok) { if (err) atomicOr(err, 256); break; }
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int s = it % kStages;
+            const uint32_t v_addr = smem_addr(kv_smem + (size_t)s * kStageBytes) + kKBytes;
             // O += P V: four k steps of 16 keys; V rows are keys, 16 keys = 2048 bytes further
 #pragma unroll
             for (int k = 0; k < kKeys / 16; ++k) {
@@ -267,7 +280,6 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 const uint64_t b = desc_mn_major(v_addr + k * 2048, kVBytes / 2);
                 umma(tmem_base + kColO, a, b, kDescO, (it | k) != 0);
             }
-            if (debug_stop == 3) break;
             umma_commit(kv_empty + s);            // the stage is free when these products are done
             umma_commit(o_full);
         }
@@ -284,55 +296,49 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         float run_max = -INFINITY, run_sum = 0.f;
         bool ok = true;
         int it = 0;
-        for (int t = t_first; t <= t_last && !*give_up && debug_stop != 1; ++t, ++it) {
-            ok = mbar_wait(s_full, it & 1);
-            if (!ok) { if (lane == 0 && err) atomicOr(err, 128); break; }
+        for (int t = t_first; t <= t_last && !*give_up; ++t, ++it) {
+            ok = mbar_wait(s_full + (it & 1), (it >> 1) & 1);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float s[64];
             {
                 float part[32];
-                tmem_load_32(lane_base + kColS, part);
+                tmem_load_32(lane_base + kColS + (it & 1) * kKeys, part);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) s[i] = part[i];
-                tmem_load_32(lane_base + kColS + 32, part);
+                tmem_load_32(lane_base + kColS + (it & 1) * kKeys + 32, part);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) s[32 + i] = part[i];
             }
-            if (debug_stop == 2) break;
             const int key0 = t * kKeys;
             float tile_max = -INFINITY;
+            // a tile that every row of this warp sees whole needs no mask
+            const int warp_first = pos0 + quarter * 32, warp_last = warp_first + 31;
+            const bool whole = key0 + kKeys - 1 <= warp_first && (window <= 0 || key0 > warp_last - window);
+            if (!whole) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const int key = key0 + i;
-                const bool visible = key <= pos && (window <= 0 || key > pos - window);
-                s[i] = visible ? s[i] * scale_log2 : -INFINITY;
-                tile_max = fmaxf(tile_max, s[i]);
-            }
-            const float new_max = fmaxf(run_max, tile_max);
-            const float base = new_max == -INFINITY ? 0.f : new_max;      // no visible key yet
-            const float corr = exp2f(run_max - base);                      // 0 on the first tile
-            run_max = new_max;
-            float sum = 0.f;
-            // P, rounded to bfloat16, into the K-major swizzled tile: row r, 16-byte chunk c at
-            // chunk (c ^ (r % 8)) of the row's 128 bytes.
-            unsigned char* p_row = p_smem + (size_t)r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 packed;
-                __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&packed);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float p = exp2f(s[c * 8 + e] - base);
-                    sum += p;
-                    pb[e] = __float2bfloat16_rn(p);
+                for (int i = 0; i < 64; ++i) {
+                    const int key = key0 + i;
+                    const bool visible = key <= pos && (window <= 0 || key > pos - window);
+                    s[i] = visible ? s[i] : -INFINITY;
                 }
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
             }
-            run_sum = run_sum * corr + sum;
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) tile_max = fmaxf(tile_max, fmaxf(s[i], s[i + 1]));
+            tile_max *= scale_log2;                                        // scale > 0: the maximum scales with it
+            // The reference point of the exponentials follows the maximum only when the maximum
+            // has moved by more than 2^8 (softmax does not depend on the reference point; P stays
+            // below 2^8, far inside bfloat16 and float32 range), so that the output accumulator
+            // in tensor memory is rescaled a few times per row instead of at nearly every tile.
+            float new_max = run_max;
+            if (tile_max > run_max + 8.0f) new_max = tile_max;
+            const float base = new_max == -INFINITY ? 0.f : new_max;      // no visible key yet
+            const float corr = fast_exp2(run_max - base);                  // 1 when unchanged, 0 on the first tile
+            run_max = new_max;
             if (it > 0) {
-                // the previous O += P V must be complete before O is rescaled
+                // the previous O += P V must be complete before P is overwritten and O rescaled
                 ok = mbar_wait(o_full, (it - 1) & 1);
-                if (!ok) { if (lane == 0 && err) atomicOr(err, 512); break; }
+                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // tcgen05.ld/st are warp-wide: the whole warp rescales if any of its rows must
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
@@ -346,13 +352,29 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                     }
                 }
             }
+            float sum = 0.f;
+            // P, rounded to bfloat16, into the K-major swizzled tile: row r, 16-byte chunk c at
+            // chunk (c ^ (r % 8)) of the row's 128 bytes.
+            unsigned char* p_row = p_smem + (size_t)r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint4 packed;
+                __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float p = fast_exp2(fmaf(s[c * 8 + e], scale_log2, -base));
+                    sum += p;
+                    pb[e] = __float2bfloat16_rn(p);
+                }
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
+            }
+            run_sum = run_sum * corr + sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
-            if (debug_stop == 3) break;
         }
-        if (ok && !*give_up && it > 0 && debug_stop == 0) {
+        if (ok && !*give_up && it > 0) {
             ok = mbar_wait(o_full, (it - 1) & 1);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -457,7 +479,6 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     }
     dim3 grid(n_tiles, n_q);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
-               tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window, err,
-               getenv("THN_DEBUG_STOP") ? atoi(getenv("THN_DEBUG_STOP")) : 0);
+               tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window, err);
     return thn_launch_status("attention_tcgen05");
 }
