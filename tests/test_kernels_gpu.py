@@ -378,12 +378,15 @@ def test_attention_window_edge(kernel, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_q,n_kv,D", [(4, 2, 16), (5, 1, 48), (8, 8, 128), (3, 3, 80)])
-def test_qk_norm_rope_cache(dtype, n_q, n_kv, D):
+@pytest.mark.parametrize("lengths,counts", [([90, 7, 64], [25, 7, 1]), ([200, 7, 64], [131, 7, 1])],
+                         ids=["few-rows", "many-rows"])
+@pytest.mark.parametrize("n_q,n_kv,D", [(4, 2, 16), (5, 1, 48), (8, 8, 128), (3, 3, 80), (5, 1, 64)])
+def test_qk_norm_rope_cache(dtype, n_q, n_kv, D, lengths, counts):
+    """Few rows and many rows take different shapes of the bfloat16 kernel (one head or
+    several heads per warp; 5 + 2 heads leave a last group that is not full)."""
     from thing_htn_2026_b200.config.base import PartSpec
     from thing_htn_2026_b200.parts import Runtime, part_class
     o = ops()
-    lengths, counts = [90, 7, 64], [25, 7, 1]
     fix = PagedFixture(n_kv, D, lengths, dtype)
     # the sequences already hold lengths - counts tokens
     old = [n - c for n, c in zip(lengths, counts)]

@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
 
     // Later tiles of a sequence see more keys and run longer: start them first, so that the
     // short ones fill the end of the grid.
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+    const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;
     const int row0 = tile_row0[tile], n_rows = tile_rows[tile];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (n_q / kv.n_kv);
@@ -505,7 +505,8 @@ int launch_prefill(void* out, const void* q, const int* tile_row0, const int* ti
         }
         configured = true;
     }
-    dim3 grid(n_tiles, n_q);
+    THN_UNSUPPORTED_IF(n_tiles > 65535, "attention_prefill: %d row tiles in one step (at most 65535)", n_tiles);
+    dim3 grid(n_q, n_tiles);
     thn_launch(attention_prefill_kernel<D>, grid, kPrefillThreads, prefill_smem<D>(), stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, tile_row0, tile_rows, row_slot, row_pos, kv, n_q,
         scale * kLog2e, window, err);
     return thn_launch_status("attention_prefill");

@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;     // long tiles first
+    const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;     // heads fastest; the list ends with the long tiles
     const int row0 = tile_row0[tile], n_rows = tile_rows[tile];
     const int kvh = h / (n_q / n_kv);
     const int pos0 = row_pos[row0], pos_last = pos0 + n_rows - 1;
@@ -335,6 +335,21 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             const float base = new_max == -INFINITY ? 0.f : new_max;      // no visible key yet
             const float corr = fast_exp2(run_max - base);                  // 1 when unchanged, 0 on the first tile
             run_max = new_max;
+            // P, rounded to bfloat16, in registers first: the exponentials run while the
+            // previous O += P V is still in the tensor core.
+            float sum = 0.f;
+            uint4 packed[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const float p0 = fast_exp2(fmaf(s[c * 8 + e], scale_log2, -base));
+                    const float p1 = fast_exp2(fmaf(s[c * 8 + e + 1], scale_log2, -base));
+                    sum += p0 + p1;
+                    pb[e / 2] = __floats2bfloat162_rn(p0, p1);
+                }
+            }
             if (it > 0) {
                 // the previous O += P V must be complete before P is overwritten and O rescaled
                 ok = mbar_wait(o_full, (it - 1) & 1);
@@ -352,22 +367,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                     }
                 }
             }
-            float sum = 0.f;
-            // P, rounded to bfloat16, into the K-major swizzled tile: row r, 16-byte chunk c at
-            // chunk (c ^ (r % 8)) of the row's 128 bytes.
+            // into the K-major swizzled tile: row r, 16-byte chunk c at chunk (c ^ (r % 8)) of
+            // the row's 128 bytes.
             unsigned char* p_row = p_smem + (size_t)r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 packed;
-                __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(&packed);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float p = fast_exp2(fmaf(s[c * 8 + e], scale_log2, -base));
-                    sum += p;
-                    pb[e] = __float2bfloat16_rn(p);
-                }
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed;
-            }
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed[c];
             run_sum = run_sum * corr + sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -460,6 +464,7 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
     THN_CHECK_ARG((((uintptr_t)q | (uintptr_t)out | (uintptr_t)kv_base) & 15) == 0,
                   "attention_tcgen05: operands must be 16-byte aligned");
     if (n_tiles == 0) return THN_OK;
+    THN_UNSUPPORTED_IF(n_tiles > 65535, "attention_tcgen05: %d row tiles in one step (at most 65535)", n_tiles);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -477,7 +482,7 @@ THN_API int thn_attention_prefill_tcgen05(void* out, const void* q, const int* t
         thn_set_error("attention_tcgen05: cuTensorMapEncodeTiled failed");
         return THN_BAD_ARGUMENT;
     }
-    dim3 grid(n_tiles, n_q);
+    dim3 grid(n_q, n_tiles);
     thn_launch(attention_tcgen05_kernel, grid, kThreads, kSmemBytes, stream, map_q, map_kv, (__nv_bfloat16*)out,
                tile_row0, tile_rows, row_slot, row_pos, block_table, bt_stride, n_kv, n_q, scale * kLog2e, window, err);
     return thn_launch_status("attention_tcgen05");

@@ -87,8 +87,14 @@ __global__ void qk_norm_rope_cache_kernel(
 
 // The serving case: bfloat16 tensor input, head sizes 64, 128 and 256, full rotation.  A lane
 // owns E = D / 64 consecutive values in each half of the head, so the partner of every value
-// it rotates is its own: no shared memory, 4-byte or wider accesses, same arithmetic.
-template <typename WT, int D>
+// it rotates is its own: no shared memory, 4-byte or wider accesses, same arithmetic.  A warp
+// takes H consecutive heads of one row: their loads are all in flight before the first is
+// used, and the row's position, page and angles are fetched once.  Steps of few rows take
+// H = 1, so that every head has a warp of its own.
+constexpr int kHeadsPerWarp = 4;
+constexpr int kFewRows = 64;
+
+template <typename WT, int D, int H>
 __global__ void qk_norm_rope_cache_bf16_kernel(
     __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ q_gain,
     const WT* __restrict__ k_gain, float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
@@ -96,66 +102,85 @@ __global__ void qk_norm_rope_cache_bf16_kernel(
     int write_cache, int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
+    using B = __nv_bfloat16;
     constexpr int E = D / 64, kHalf = D / 2;
     const int lane = threadIdx.x & 31;
     const int n_heads_total = n_q + 2 * kv.n_kv;
+    const int groups = (n_heads_total + H - 1) / H;
     const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (unit >= (long long)n_rows * n_heads_total) return;
-    const int m = (int)(unit / n_heads_total), head = (int)(unit - (long long)m * n_heads_total);
-    const bool is_q = head < n_q, is_k = !is_q && head < n_q + kv.n_kv;
-    if (!is_q && !write_cache) return;
-    const __nv_bfloat16* src = qkv + (size_t)m * n_heads_total * D + (size_t)head * D;
-    const int pos = row_pos[m];
-
-    __nv_bfloat16* dst;
-    if (is_q) {
-        dst = q_out + (size_t)m * n_q * D + (size_t)head * D;
-    } else {
-        const int kvh = is_k ? head - n_q : head - n_q - kv.n_kv;
-        const int page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
-        if (page < 0) {
-            if (lane == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
-            return;
-        }
-        dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, is_k ? 0 : 1, kvh, pos % kv.page_size);
-    }
+    if (unit >= (long long)n_rows * groups) return;
+    const int m = (int)(unit / groups), head0 = (int)(unit - (long long)m * groups) * H;
+    const int n_here = min(H, (write_cache ? n_heads_total : n_q) - head0);
+    if (n_here <= 0) return;
+    const __nv_bfloat16* src = qkv + (size_t)m * n_heads_total * D + (size_t)head0 * D;
     const int d0 = lane * E;                       // this lane's values: [d0, d0 + E) and [kHalf + d0, ...)
-    __nv_bfloat16 lo[E], hi[E];
+    __nv_bfloat16 lo[H][E], hi[H][E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-        lo[e] = src[d0 + e];
-        hi[e] = src[kHalf + d0 + e];
-    }
-    if (!is_q && !is_k) {                          // V: plain copy
+    for (int i = 0; i < H; ++i) {
+        if (i < n_here) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            dst[d0 + e] = lo[e];
-            dst[kHalf + d0 + e] = hi[e];
+            for (int e = 0; e < E; ++e) {
+                lo[i][e] = src[(size_t)i * D + d0 + e];
+                hi[i][e] = src[(size_t)i * D + kHalf + d0 + e];
+            }
         }
-        return;
     }
+    const int pos = row_pos[m];
     if (pos >= table_len) {
         if (lane == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
         return;
     }
-    const WT* gain = is_q ? q_gain : k_gain;
-    float a[E], b[E], ss = 0.f;
+    float c[E], sn[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-        a[e] = __bfloat162float(lo[e]);
-        b[e] = __bfloat162float(hi[e]);
-        ss += a[e] * a[e] + b[e] * b[e];
+        c[e] = rnd<B>(cos_tab[(size_t)pos * kHalf + d0 + e]);
+        sn[e] = rnd<B>(sin_tab[(size_t)pos * kHalf + d0 + e]);
     }
-    ss = warp_sum(ss);
-    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    int page = 0;
+    if (head0 + n_here > n_q) {
+        page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
+        if (page < 0) {
+            if (lane == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            return;
+        }
+    }
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-        using B = __nv_bfloat16;
-        const float x0 = rnd<B>(to_f32<WT>(gain[d0 + e]) * rnd<B>(a[e] * rstd));
-        const float x1 = rnd<B>(to_f32<WT>(gain[kHalf + d0 + e]) * rnd<B>(b[e] * rstd));
-        const float c = rnd<B>(cos_tab[(size_t)pos * kHalf + d0 + e]), s = rnd<B>(sin_tab[(size_t)pos * kHalf + d0 + e]);
-        dst[d0 + e] = __float2bfloat16_rn(rnd<B>(x0 * c) + rnd<B>(-x1 * s));
-        dst[kHalf + d0 + e] = __float2bfloat16_rn(rnd<B>(x1 * c) + rnd<B>(x0 * s));
+    for (int i = 0; i < H; ++i) {
+        if (i >= n_here) break;
+        const int head = head0 + i;                // the same for the whole warp
+        const bool is_q = head < n_q, is_k = !is_q && head < n_q + kv.n_kv;
+        __nv_bfloat16* dst;
+        if (is_q) {
+            dst = q_out + (size_t)m * n_q * D + (size_t)head * D;
+        } else {
+            const int kvh = is_k ? head - n_q : head - n_q - kv.n_kv;
+            dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, is_k ? 0 : 1, kvh, pos % kv.page_size);
+        }
+        if (!is_q && !is_k) {                      // V: plain copy
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                dst[d0 + e] = lo[i][e];
+                dst[kHalf + d0 + e] = hi[i][e];
+            }
+            continue;
+        }
+        const WT* gain = is_q ? q_gain : k_gain;
+        float a[E], b[E], ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            a[e] = __bfloat162float(lo[i][e]);
+            b[e] = __bfloat162float(hi[i][e]);
+            ss += a[e] * a[e] + b[e] * b[e];
+        }
+        ss = warp_sum(ss);
+        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float x0 = rnd<B>(to_f32<WT>(gain[d0 + e]) * rnd<B>(a[e] * rstd));
+            const float x1 = rnd<B>(to_f32<WT>(gain[kHalf + d0 + e]) * rnd<B>(b[e] * rstd));
+            dst[d0 + e] = __float2bfloat16_rn(rnd<B>(x0 * c[e]) + rnd<B>(-x1 * sn[e]));
+            dst[kHalf + d0 + e] = __float2bfloat16_rn(rnd<B>(x1 * c[e]) + rnd<B>(x0 * sn[e]));
+        }
     }
 }
 
@@ -185,10 +210,18 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
     const long long part_stride = (long long)n_rows * (n_q + 2 * n_kv) * head_dim;
     if (dtype == THN_BF16 && qkv && q_gain && cos_tab && rotary_dim == head_dim &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
-#define FAST(WT, D)                                                                                                 \
-    thn_launch(qk_norm_rope_cache_bf16_kernel<WT, D>, blocks, warps * 32, 0, stream, \
+        const int per_warp = n_rows <= kFewRows ? 1 : kHeadsPerWarp;
+        const long long fast_units = (long long)n_rows * ((n_q + 2 * n_kv + per_warp - 1) / per_warp);
+        const unsigned fast_blocks = (unsigned)((fast_units + warps - 1) / warps);
+#define FAST_H(WT, D, H)                                                                                            \
+    thn_launch(qk_norm_rope_cache_bf16_kernel<WT, D, H>, fast_blocks, warps * 32, 0, stream, \
         (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, (const WT*)q_gain, (const WT*)k_gain, eps, cos_tab,       \
         sin_tab, table_len, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)
+#define FAST(WT, D)                                                                                                 \
+    do {                                                                                                            \
+        if (per_warp == 1) FAST_H(WT, D, 1);                                                                        \
+        else FAST_H(WT, D, kHeadsPerWarp);                                                                          \
+    } while (0)
         bool done = true;
         if (w_dtype == THN_BF16 && head_dim == 64) FAST(__nv_bfloat16, 64);
         else if (w_dtype == THN_BF16 && head_dim == 128) FAST(__nv_bfloat16, 128);
@@ -198,6 +231,7 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
         else if (w_dtype == THN_F32 && head_dim == 256) FAST(float, 256);
         else done = false;
 #undef FAST
+#undef FAST_H
         if (done) return thn_launch_status("qk_norm_rope_cache");
     }
 #define LAUNCH(T, WT)                                                                                              \

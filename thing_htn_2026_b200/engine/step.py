@@ -84,11 +84,19 @@ class StepRunner:
         tile_row0: List[int] = []
         tile_rows: List[int] = []
         if max(counts) > 1:
+            # Row tiles for the prompt attention kernels, the ones that see the fewest keys
+            # first: the kernels start at the end of the list, so the longest run first and
+            # the short ones fill the gaps at the end.
             size = ops.ROW_TILE()
-            for start, c in zip(cu, counts):
+            tiles = []
+            for slot, start, c in zip(slots, cu, counts):
+                held = self.cache.length(slot)
                 for r in range(0, c, size):
-                    tile_row0.append(start + r)
-                    tile_rows.append(min(size, c - r))
+                    n = min(size, c - r)
+                    tiles.append((held + r + n, start + r, n))
+            tiles.sort()
+            tile_row0 = [t[1] for t in tiles]
+            tile_rows = [t[2] for t in tiles]
 
         parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows, tile_row0, tile_rows]
         packed = self._upload([x for part in parts for x in part])
