@@ -85,6 +85,7 @@ def main():
     dev = "cuda:0"
     m = args.batch
     results = {}
+    err = ops.new_error_word(dev)
 
     shapes = {"qkv": ((NQ + 2 * NKV) * D, H), "o": (H, NQ * D), "gate_up": (2 * I, H), "down": (H, I),
               "lm_head": (V, H)}
@@ -98,8 +99,16 @@ def main():
             us = time_cold(lambda i: ops.linear_smallm(x, weights[i]), copies, args.reps)
             entry["own_us"], entry["own_gbs"] = us, nbytes / us / 1e3
             entry["span"], entry["slabs"] = ops.smallm_plan(m, n, k, dev)
+        if ops.lib().thn_gemm_stream_supported(m, n, k):
+            us = time_cold(lambda i: ops.linear_stream(x, weights[i], err=err), copies, args.reps)
+            entry["stream_us"], entry["stream_gbs"] = us, nbytes / us / 1e3
         us = time_cold(lambda i: torch.nn.functional.linear(x, weights[i]), copies, args.reps)
         entry["library_us"], entry["library_gbs"] = us, nbytes / us / 1e3
+        if name == "gate_up" and ops.lib().thn_gemm_stream_supported(m, n // 2, k):
+            entry["stream_fused_swiglu_us"] = time_cold(
+                lambda i: ops.linear_stream(x, weights[i], err=err, swiglu=True), copies, args.reps)
+            entry["library_plus_swiglu_us"] = time_cold(
+                lambda i: ops.swiglu(torch.nn.functional.linear(x, weights[i])), copies, args.reps)
         results[f"gemm_{name}_m{m}"] = entry
         del weights
 
@@ -121,7 +130,6 @@ def main():
     cu1 = torch.arange(m + 1, dtype=torch.int32, device=dev)
     rows = ops.step_rows(cu1, slots_dev, cache.seq_lens, m, 1)
     q = torch.randn(m, NQ * D, device=dev, dtype=torch.bfloat16)
-    err = ops.new_error_word(dev)
     views = [cache.kv_view(e) for e in range(n_copies)]
     for view in views:
         view.storage.normal_()
@@ -140,6 +148,7 @@ def main():
     results["swiglu"] = {"own_us": time_cold(lambda i: ops.swiglu(gu), 1, args.reps)}
     logits = torch.randn(m, V, device=dev, dtype=torch.float32)
     results["choose_tokens"] = {"own_us": time_cold(lambda i: ops.choose_tokens(logits), 1, args.reps)}
+    assert int(err.item()) == 0, "a kernel reported an error"
     for name, entry in results.items():
         print(name, json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in entry.items()}))
 

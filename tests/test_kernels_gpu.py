@@ -121,6 +121,54 @@ def test_gemm_smallm(m, n, k):
     assert o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).dtype == torch.float32
 
 
+@pytest.mark.parametrize("m", [1, 8, 9, 16, 17, 40, 64])
+@pytest.mark.parametrize("n,k", [(100, 64), (2560, 4096), (6144, 2560), (77, 648), (2560, 9728), (300, 72)])
+def test_gemm_stream(m, n, k):
+    """The TMA / tcgen05 weight-streaming product against a float64 product, with the work cut
+    for the whole GPU and for odd numbers of blocks (tiles shared by 1 to many blocks, runs
+    that start and end inside tiles, N and K that leave ragged tiles); the result does not
+    depend on the run at all, and a row does not depend on the rows beside it."""
+    o = ops()
+    x, w = rand((m, k), torch.bfloat16, 60), rand((n, k), torch.bfloat16, 61, 0.05)
+    exact = x.double() @ w.double().t()
+    bound = 2e-6 * k ** 0.5 * max(1.0, exact.abs().max().item())
+    err = o.new_error_word(DEV)
+    xd, wd = x.to(DEV), w.to(DEV)
+    for n_blocks in [0, 1, 7, 1000]:
+        out32 = o.linear_stream(xd, wd, torch.float32, err=err, n_blocks=n_blocks)
+        assert int(err.item()) == 0, "a pipeline wait timed out"
+        worst = (out32.double().cpu() - exact).abs().max().item()
+        assert worst <= bound, f"n_blocks {n_blocks}: error {worst:.3e}"
+        out16 = o.linear_stream(xd, wd, err=err, n_blocks=n_blocks)
+        assert torch.equal(out16, out32.to(torch.bfloat16)), "bfloat16 output is the float32 sum rounded once"
+        again = o.linear_stream(xd, wd, torch.float32, err=err, n_blocks=n_blocks)
+        assert torch.equal(again, out32), "two runs differ: the order of the sum depends on timing"
+    whole = o.linear_stream(xd, wd, torch.float32, err=err)
+    alone = o.linear_stream(xd[m - 1:].contiguous(), wd, torch.float32, err=err)
+    assert torch.equal(whole[m - 1:], alone), "a row depends on its batch mates"
+    assert int(err.item()) == 0
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 128, 64), (8, 9728, 2560), (13, 200, 136), (33, 384, 200), (64, 1000, 512)])
+def test_gemm_stream_fused_swiglu(m, inter, k):
+    """Gate/up product and SwiGLU in one weight-streaming kernel against the two plain steps;
+    the measure is the one of the many-row fused kernel."""
+    o = ops()
+    x, w = rand((m, k), torch.bfloat16, 62), rand((2 * inter, k), torch.bfloat16, 63, 0.05)
+    err = o.new_error_word(DEV)
+    gu = x.float() @ w.float().t()
+    want = plain.swiglu(gu[:, :inter].to(torch.bfloat16), gu[:, inter:].to(torch.bfloat16), torch.bfloat16).float()
+    exact = plain.swiglu(gu[:, :inter], gu[:, inter:], torch.float32)
+    noise = (want - exact).abs()
+    step = torch.exp2(torch.floor(torch.log2(want.abs().clamp_min(1e-30))) - 7)
+    for n_blocks in [0, 5]:
+        out = o.linear_stream(x.to(DEV), w.to(DEV), err=err, swiglu=True, n_blocks=n_blocks).float().cpu()
+        assert int(err.item()) == 0, "a pipeline wait timed out"
+        err_abs = (out - want).abs()
+        assert (err_abs - step).max() <= noise.max(), f"{(err_abs - step).max():.3e} beyond a rounding step"
+        assert err_abs.pow(2).mean().sqrt() <= noise.pow(2).mean().sqrt() + 1e-12
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (100, 200, 72), (300, 1000, 136), (2048, 2560, 4096), (513, 6144, 2560),
                                    (64, 2560, 9728)])
 def test_gemm_tcgen05(m, n, k):

@@ -132,7 +132,7 @@ class DeviceBackend:
                              out=(self.row_slot[:batch], self.row_pos[:batch]))
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
         h, d = self.model.hidden(tokens, ctx)
-        logits = self.model.logits(h, d, None)
+        logits = self.model.logits(h, d, None, self.err)
         self._choose(logits, slots, self.out_tokens[:batch])
         ops.advance(self.cache.seq_lens, slots, cu)
 

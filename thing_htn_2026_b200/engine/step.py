@@ -112,7 +112,7 @@ class StepRunner:
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
         h, d = self.model.hidden(tokens, ctx)
         if want_rows:
-            logits = self.model.logits(h, d, want_dev)
+            logits = self.model.logits(h, d, want_dev, self.err)
         else:
             logits = torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
         ops.advance(self.cache.seq_lens, slots_dev, cu_dev)

@@ -92,14 +92,16 @@ class DecoderModel:
             h, d = self.layers[entry.layer].forward(h, d, ctx, entry)
         return h, d
 
-    def logits(self, h: torch.Tensor, d: Optional[torch.Tensor], rows: Optional[torch.Tensor]) -> torch.Tensor:
-        """Final norm and head at the given rows (int32 indices; None: every row): float32."""
+    def logits(self, h: torch.Tensor, d: Optional[torch.Tensor], rows: Optional[torch.Tensor],
+               err: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Final norm and head at the given rows (int32 indices; None: every row): float32.
+        ``err``: the step's device error word."""
         if rows is not None:
             h = ops.gather_rows(h, rows)
             d = ops.gather_rows(ops.resolve(d), rows) if d is not None else None
         n = self.final_norm.forward(h) if d is None else self.final_norm.add_forward(h, d)
-        return self.head.forward(n)
+        return self.head.forward(n, err)
 
     def forward(self, tokens: torch.Tensor, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         h, d = self.hidden(tokens, ctx)
-        return self.logits(h, d, want_rows)
+        return self.logits(h, d, want_rows, ctx.err)

@@ -43,6 +43,10 @@ _SIGNATURES = {
     "thn_gemm_smallm_supported": [c_int, c_int, c_int],
     "thn_gemm_tcgen05_supported": [c_int, c_int, c_int],
     "thn_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_gemm_stream_supported": [c_int, c_int, c_int],
+    "thn_gemm_stream_scratch": [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p, c_void_p],
     "thn_gemm_smallm_plan": [c_int, c_int, c_int, c_int, c_int, c_void_p],
     "thn_gemm_smallm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_void_p],
@@ -361,6 +365,45 @@ def linear_smallm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     return out
 
 
+_stream_needs = {}
+_stream_counters = {}
+
+
+def _stream_need(m: int, n: int, k: int, swiglu: bool, n_blocks: int):
+    key = (m, n, k, swiglu, n_blocks)
+    if key not in _stream_needs:
+        floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
+        lib().thn_gemm_stream_scratch(m, n, k, int(swiglu), n_blocks, ctypes.byref(floats), ctypes.byref(counters))
+        _stream_needs[key] = (floats.value, counters.value)
+    return _stream_needs[key]
+
+
+def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                  swiglu: bool = False, err: Optional[torch.Tensor] = None, n_blocks: int = 0) -> torch.Tensor:
+    """The TMA / tcgen05 weight-streaming product for steps of at most 64 rows (bfloat16
+    operands, K a multiple of 8) -> ``[M, N]`` in bfloat16 or float32.  With ``swiglu`` the
+    weight is ``[2 * I, K]`` (gate rows, then up rows) and the result is ``silu(gate) * up``,
+    ``[M, I]``, in one kernel.  ``n_blocks`` overrides the number of blocks the work is cut
+    for (tests; default: one per SM)."""
+    _need(x, "linear_stream x", torch.bfloat16)
+    _need(weight, "linear_stream weight", torch.bfloat16)
+    m, k = x.shape
+    n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    if weight.shape[1] != k or (swiglu and weight.shape[0] % 2):
+        raise KernelError(f"linear_stream: shapes x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    floats, n_counters = _stream_need(m, n, k, swiglu, n_blocks)
+    index = x.device.index or 0
+    counters = _stream_counters.get(index)
+    if counters is None or counters.numel() < n_counters:
+        counters = torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device=x.device)   # graphs keep its address
+        _stream_counters[index] = counters
+    scratch = torch.empty(floats, dtype=torch.float32, device=x.device)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _call("thn_gemm_stream_bf16", _ptr(out), DTYPE_CODE[out_dtype], _ptr(scratch), _ptr(counters), _ptr(x),
+          _ptr(weight), m, n, k, int(swiglu), n_blocks, _ptr(err), _stream())
+    return out
+
+
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, err: Optional[torch.Tensor] = None,
                    swiglu: bool = False) -> torch.Tensor:
     """The tcgen05 / TMEM / TMA product for steps with many rows: ``x [M, K] @ weight[N, K]^T``
@@ -377,7 +420,31 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, err: Optional[torch.Te
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False):
+STREAM_POLICY = os.environ.get("THN_LINEAR_STREAM", "auto")
+
+
+def _stream_takes(m: int, n: int, k: int, fused: bool = False) -> bool:
+    if not lib().thn_gemm_stream_supported(m, n, k):
+        return False
+    if STREAM_POLICY in ("all", "none"):
+        return STREAM_POLICY == "all"
+    if STREAM_POLICY == "deep":
+        return k >= SMALLM_MIN_K or n >= 65536
+    if STREAM_POLICY == "fused":
+        return fused or k >= SMALLM_MIN_K or n >= 65536
+    return False
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for ``w_gate_up = cat(gate, up)``: one kernel where the
+    weight-streaming product takes the shape, else the product followed by the activation."""
+    if x.dtype == torch.bfloat16 and _stream_takes(x.shape[0], w_gate_up.shape[0] // 2, x.shape[1], fused=True):
+        return linear_stream(x, w_gate_up, swiglu=True, err=err)
+    return swiglu(linear(x, w_gate_up, split_ok=True, err=err))
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False,
+           err: Optional[torch.Tensor] = None):
     """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
     rows: this library's weight-streaming kernel.  bfloat16 otherwise: the vendor library's
     tensor-core product with float32 accumulation (the reference's choice,
@@ -394,6 +461,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return out
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: dtype {x.dtype} is not supported")
+    if _stream_takes(x.shape[0], weight.shape[0], x.shape[1]):
+        return linear_stream(x, weight, out_dtype or torch.bfloat16, err=err)
     if x.shape[1] >= SMALLM_MIN_K and lib().thn_gemm_smallm_supported(x.shape[0], weight.shape[0], x.shape[1]):
         return linear_smallm(x, weight, out_dtype or torch.bfloat16)
     if out_dtype in (None, torch.bfloat16):

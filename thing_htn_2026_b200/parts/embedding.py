@@ -4,7 +4,7 @@ Logits are float32."""
 
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -40,5 +40,5 @@ class LMHead:
         self.weight = runtime.tensor(spec, "weight")
         self.vocab_size = int(spec.params["vocab_size"])
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=torch.float32)
+    def forward(self, x: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, out_dtype=torch.float32, err=err)

@@ -29,4 +29,5 @@ class SwiGLU:
         self.w_down = runtime.tensor(spec, "down_proj")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up, split_ok=True)), self.w_down, split_ok=True)
+        err = getattr(ctx, "err", None)
+        return ops.linear(ops.linear_swiglu(x, self.w_gate_up, err), self.w_down, split_ok=True, err=err)
