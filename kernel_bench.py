@@ -95,10 +95,6 @@ def main():
         x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
         nbytes = n * k * 2
         entry = {"bytes": nbytes, "copies": copies}
-        if ops.lib().thn_gemm_smallm_supported(m, n, k):
-            us = time_cold(lambda i: ops.linear_smallm(x, weights[i]), copies, args.reps)
-            entry["own_us"], entry["own_gbs"] = us, nbytes / us / 1e3
-            entry["span"], entry["slabs"] = ops.smallm_plan(m, n, k, dev)
         if ops.lib().thn_gemm_stream_supported(m, n, k):
             us = time_cold(lambda i: ops.linear_stream(x, weights[i], err=err), copies, args.reps)
             entry["stream_us"], entry["stream_gbs"] = us, nbytes / us / 1e3

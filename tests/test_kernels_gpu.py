@@ -100,41 +100,21 @@ def test_rope_table_matches_formula():
         assert (t.sin[:3000].cpu() - sin[:, :head_dim // 2]).abs().max() <= 2e-6
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(100, 64), (2560, 4096), (6144, 2560), (77, 640), (19456, 2560), (2560, 9728)])
-def test_gemm_smallm(m, n, k):
-    """The weight-streaming product for few rows against a float64 product, with the work
-    cut for the whole GPU and for odd numbers of warps (tiles shared by 1 to 8 warps); the
-    result does not depend on the cut beyond float32 order, and not at all on the run."""
-    o = ops()
-    x, w = rand((m, k), torch.bfloat16, 40), rand((n, k), torch.bfloat16, 41, 0.05)
-    exact = x.double() @ w.double().t()
-    bound = 2e-6 * k ** 0.5 * max(1.0, exact.abs().max().item())
-    for n_warps in [0, 7, 1000, 100000]:
-        out32 = o.linear_smallm(x.to(DEV), w.to(DEV), torch.float32, n_warps=n_warps)
-        err = (out32.double().cpu() - exact).abs().max().item()
-        assert err <= bound, f"n_warps {n_warps}: error {err:.3e}"
-        out16 = o.linear_smallm(x.to(DEV), w.to(DEV), n_warps=n_warps)
-        assert torch.equal(out16, out32.to(torch.bfloat16)), "bfloat16 output is the float32 sum rounded once"
-        again = o.linear_smallm(x.to(DEV), w.to(DEV), torch.float32, n_warps=n_warps)
-        assert torch.equal(again, out32), "two runs differ: the order of the sum depends on timing"
-    assert o.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).dtype == torch.float32
-
-
 @pytest.mark.parametrize("m", [1, 8, 9, 16, 17, 40, 64])
 @pytest.mark.parametrize("n,k", [(100, 64), (2560, 4096), (6144, 2560), (77, 648), (2560, 9728), (300, 72)])
 def test_gemm_stream(m, n, k):
     """The TMA / tcgen05 weight-streaming product against a float64 product, with the work cut
     for the whole GPU and for odd numbers of blocks (tiles shared by 1 to many blocks, runs
-    that start and end inside tiles, N and K that leave ragged tiles); the result does not
-    depend on the run at all, and a row does not depend on the rows beside it."""
+    that start and end inside tiles, N and K that leave ragged tiles) and with each tile cut
+    along K inside a thread-block cluster; the result does not depend on the run at all, and
+    a row does not depend on the rows beside it."""
     o = ops()
     x, w = rand((m, k), torch.bfloat16, 60), rand((n, k), torch.bfloat16, 61, 0.05)
     exact = x.double() @ w.double().t()
     bound = 2e-6 * k ** 0.5 * max(1.0, exact.abs().max().item())
     err = o.new_error_word(DEV)
     xd, wd = x.to(DEV), w.to(DEV)
-    for n_blocks in [0, 1, 7, 1000]:
+    for n_blocks in [0, 1, 7, 1000, -2, -6]:           # negative: a thread-block cluster of that size per tile
         out32 = o.linear_stream(xd, wd, torch.float32, err=err, n_blocks=n_blocks)
         assert int(err.item()) == 0, "a pipeline wait timed out"
         worst = (out32.double().cpu() - exact).abs().max().item()

@@ -7,9 +7,9 @@
 // by the block size, so a row's result does not depend on the batch it is in.
 //
 // Inputs that come from a matrix product may arrive as split-K partial sums (float32
-// [parts, rows, width], see gemm_smallm.cu): the kernel adds the parts in ascending order
-// and rounds the sum to the activation type, which is the value the product would have
-// stored.
+// [parts, rows, width]): the kernel adds the parts in ascending order and rounds the sum to
+// the activation type, which is the value the product would have stored.  The products of
+// this library add their own partials, so nothing on the product path uses this today.
 #include <cstdarg>
 #include <cstdio>
 

@@ -386,6 +386,165 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
     }
 }
 
+// Few tiles (N small against the number of SMs): every tile is cut along K among the blocks
+// of one thread-block cluster, one tile per cluster, and the partial sums meet in distributed
+// shared memory instead of global memory: each block parks its partial in its own shared
+// memory, the cluster's hardware barrier orders it, and block q of the cluster adds, in
+// ascending k order, the columns j = q, q + cluster size, ... of every block's partial and
+// stores them.  The second barrier keeps every block's shared memory alive until all have read.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float load_from_block(const float* mine, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(mine)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int NX, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ out,
+    int M, int N, int chunks, int* __restrict__ err) {
+    using S = Shape<NX, 0>;
+    pdl_launch_dependents();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)S::kStages * S::kStageBytes);
+    uint64_t* empty = full + S::kStages;
+    uint64_t* acc_full = empty + S::kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* partial = reinterpret_cast<float*>(tiles);      // [column][row of the tile], over the drained stages
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank(), n_ranks = (int)cluster_size();
+    const int tile = blockIdx.x / n_ranks;
+    const int c0 = (int)((long long)chunks * rank / n_ranks), c1 = (int)((long long)chunks * (rank + 1) / n_ranks);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(acc_full, 1);
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
+                     "r"(S::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        // ---- TMA producer: W of the first stages before the wait for the kernel that makes x
+        auto load_w = [&](int s, int c) {
+            mbar_expect_tx(full + s, S::kStageBytes);
+            tma_load_2d(tiles + (size_t)s * S::kStageBytes, &map_w, full + s, c * BK, tile * BW);
+        };
+        auto load_x = [&](int s, int c) {
+            tma_load_2d(tiles + (size_t)s * S::kStageBytes + kWBytes, &map_x, full + s, c * BK, 0);
+        };
+        const int early = min(S::kStages, c1 - c0);
+        for (int i = 0; i < early; ++i) load_w(i, c0 + i);
+        pdl_wait();
+        for (int i = 0; i < early; ++i) load_x(i, c0 + i);
+        int it = early;
+        for (int c = c0 + early; c < c1 && !*give_up; ++c, ++it) {
+            const int s = it % S::kStages;
+            if (!mbar_wait(empty + s, ((it / S::kStages) & 1) ^ 1)) {
+                if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                *give_up = 1;
+                break;
+            }
+            load_w(s, c);
+            load_x(s, c);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        bool ok = true;
+        int it = 0;
+        for (int c = c0; c < c1 && ok && !*give_up; ++c, ++it) {
+            const int s = it % S::kStages;
+            ok = mbar_wait(full + s, (it / S::kStages) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t w_addr = smem_addr(tiles + (size_t)s * S::kStageBytes);
+            const uint64_t w_desc = smem_desc(w_addr), x_desc = smem_desc(w_addr + kWBytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+                umma(tmem_base, w_desc + 2 * k, x_desc + 2 * k, S::kInstrDesc, (c != c0) | (k != 0));
+            umma_commit(empty + s);
+        }
+        umma_commit(acc_full);
+        if (!ok) {
+            if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+            *give_up = 1;
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue, first half: this block's partial into its shared memory
+        pdl_wait();
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        float acc[NX];
+#pragma unroll
+        for (int j = 0; j < NX; ++j) acc[j] = 0.f;
+        if (c1 > c0) {
+            if (mbar_wait(acc_full, 0)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+                for (int c = 0; c < NX; c += 16) tmem_load_16(taddr + c, acc + c);
+                tmem_wait_load();
+            } else {
+                if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                *give_up = 1;
+            }
+        }
+        // every product has been committed, so no stage is being read or written any more
+#pragma unroll
+        for (int j = 0; j < NX; ++j)
+            if (j < M) partial[j * BW + r] = acc[j];
+    }
+    cluster_sync();
+    if (warp >= 2) {
+        // ---- epilogue, second half: this block's share of the columns, summed over the cluster
+        const int r = (warp & 3) * 32 + lane;
+        const int n = tile * BW + r;
+        for (int j = rank; j < M; j += n_ranks) {
+            float sum = 0.f;
+            for (int q = 0; q < n_ranks; ++q) sum += load_from_block(partial + j * BW + r, (uint32_t)q);
+            if (n < N) out[(size_t)j * N + n] = from_f32<OutT>(sum);
+        }
+    }
+    cluster_sync();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::kTmemCols) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -465,6 +624,79 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, float*
     return thn_launch_status("gemm_stream");
 }
 
+// The largest cluster size (2 to 8) of which n_tiles clusters are resident at once, or 0.
+template <int NX, typename OutT>
+int cluster_size_for(int n_tiles) {
+    using S = Shape<NX, 0>;
+    static int resident[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};     // clusters of each size that fit
+    if (resident[0] < 0) {
+        resident[0] = 0;
+        if (cudaFuncSetAttribute(gemm_stream_cluster_kernel<NX, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)S::kSmemBytes) != cudaSuccess) {
+            cudaGetLastError();
+            for (int c = 1; c <= 8; ++c) resident[c] = 0;
+        }
+    }
+    for (int c = 8; c >= 2; --c) {
+        if (resident[c] < 0) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3((unsigned)(c * 64));
+            config.blockDim = dim3(kThreads);
+            config.dynamicSmemBytes = S::kSmemBytes;
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeClusterDimension;
+            attribute[0].val.clusterDim.x = (unsigned)c;
+            attribute[0].val.clusterDim.y = 1;
+            attribute[0].val.clusterDim.z = 1;
+            config.attrs = attribute;
+            config.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_stream_cluster_kernel<NX, OutT>, &config) != cudaSuccess) {
+                cudaGetLastError();
+                n = 0;
+            }
+            resident[c] = n;
+        }
+        if (resident[c] >= n_tiles) return c;
+    }
+    return 0;
+}
+
+template <int NX, typename OutT>
+int launch_cluster(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M, int N, int chunks, int n_tiles,
+                   int c, int* err, cudaStream_t stream) {
+    using S = Shape<NX, 0>;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)(n_tiles * c));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = S::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = (unsigned)c;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = g_thn_pdl ? 2 : 1;
+    cudaLaunchKernelEx(&config, gemm_stream_cluster_kernel<NX, OutT>, map_w, map_x, (OutT*)out, M, N, chunks, err);
+    return thn_launch_status("gemm_stream (cluster)");
+}
+
+// The cluster size to use for a shape: n_blocks < 0 asks for exactly -n_blocks (tests);
+// n_blocks == 0 takes the largest that keeps every tile's cluster resident, if the tiles are
+// few enough to need the split (fewer than half the SMs) and the blocks many enough to
+// stream at full rate; 0: the balanced runs through global memory.
+template <int NX, typename OutT>
+int choose_cluster(int n_tiles, int chunks, int n_blocks) {
+    if (n_blocks > 0) return 0;
+    const int best = cluster_size_for<NX, OutT>(n_tiles);
+    if (n_blocks < 0) return (-n_blocks >= 2 && -n_blocks <= best) ? -n_blocks : 0;
+    if (best < 2 || n_tiles * 2 > sm_count() || n_tiles * best * 3 < sm_count() * 2 || chunks < best) return 0;
+    return best;
+}
+
 }  // namespace
 
 // 1 if thn_gemm_stream_bf16 takes this shape: at most 64 rows, K a multiple of 8 (TMA wants
@@ -475,7 +707,7 @@ THN_API int thn_gemm_stream_supported(int M, int N, int K) { return M >= 1 && M 
 // first call; the kernel leaves them zero).  n_blocks <= 0: one block per SM.
 THN_API int thn_gemm_stream_scratch(int M, int N, int K, int swiglu, int n_blocks, long long* scratch_floats,
                                     int* n_counters) {
-    const Plan p = plan_for(N, K, n_blocks);
+    const Plan p = plan_for(N, K, n_blocks > 0 ? n_blocks : 0);
     *scratch_floats = (long long)p.blocks * 2 * padded_rows(M) * (swiglu ? 2 : 1) * BW;
     *n_counters = 4 * ((N + BW - 1) / BW);
     return THN_OK;
@@ -484,6 +716,8 @@ THN_API int thn_gemm_stream_scratch(int M, int N, int K, int swiglu, int n_block
 // out [M, N] (bfloat16, or float32 with out_dtype THN_F32) = x [M, K] @ w [N, K]^T; with
 // swiglu != 0, w is [2 * N, K] (gate rows, then up rows) and out = silu(x gate^T) * (x up^T).
 // scratch and counters as thn_gemm_stream_scratch says.  All pointers 16-byte aligned.
+// n_blocks: 0 lets the library choose between balanced runs on every SM and one cluster per
+// tile; > 0 cuts balanced runs for that many blocks; < 0 asks for clusters of -n_blocks.
 // err: device error word (THN_ERR_WAIT_TIMEOUT if a pipeline wait gave up).
 THN_API int thn_gemm_stream_bf16(void* out, int out_dtype, float* scratch, int* counters, const void* x, const void* w,
                                  int M, int N, int K, int swiglu, int n_blocks, int* err, cudaStream_t stream) {
@@ -494,16 +728,24 @@ THN_API int thn_gemm_stream_bf16(void* out, int out_dtype, float* scratch, int* 
     THN_CHECK_ARG(out_dtype == THN_F32 || out_dtype == THN_BF16, "gemm_stream: unknown output dtype %d", out_dtype);
     THN_CHECK_ARG(scratch != nullptr && counters != nullptr, "gemm_stream: scratch and counters, please");
     THN_UNSUPPORTED_IF(swiglu && out_dtype != THN_BF16, "gemm_stream: fused SwiGLU stores bfloat16 only");
-    const Plan p = plan_for(N, K, n_blocks);
+    const Plan p = plan_for(N, K, n_blocks > 0 ? n_blocks : 0);
     const int nx = padded_rows(M);
     CUtensorMap map_w, map_x;
     if (!make_map(&map_w, w, swiglu ? 2LL * N : N, K, BW) || !make_map(&map_x, x, M, K, nx)) {
         thn_set_error("gemm_stream: cuTensorMapEncodeTiled failed for M=%d N=%d K=%d", M, N, K);
         return THN_BAD_ARGUMENT;
     }
+    const int n_tiles = (N + BW - 1) / BW;
+#define CLUSTER(NX, OutT)                                                                                           \
+    do {                                                                                                            \
+        const int c = choose_cluster<NX, OutT>(n_tiles, p.chunks, n_blocks);                                        \
+        if (c) return launch_cluster<NX, OutT>(map_w, map_x, out, M, N, p.chunks, n_tiles, c, err, stream);         \
+    } while (0)
 #define GO(NX)                                                                                                      \
     do {                                                                                                            \
         if (swiglu) return launch<NX, 1, __nv_bfloat16>(map_w, map_x, out, scratch, counters, M, N, p, err, stream); \
+        if (out_dtype == THN_BF16) CLUSTER(NX, __nv_bfloat16);                                                      \
+        else CLUSTER(NX, float);                                                                                    \
         if (out_dtype == THN_BF16)                                                                                  \
             return launch<NX, 0, __nv_bfloat16>(map_w, map_x, out, scratch, counters, M, N, p, err, stream);        \
         return launch<NX, 0, float>(map_w, map_x, out, scratch, counters, M, N, p, err, stream);                    \
@@ -512,4 +754,5 @@ THN_API int thn_gemm_stream_bf16(void* out, int out_dtype, float* scratch, int* 
     if (nx == 32) GO(32);
     GO(64);
 #undef GO
+#undef CLUSTER
 }

@@ -40,16 +40,12 @@ _SIGNATURES = {
                     c_void_p],
     "thn_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "thn_resolve_parts": [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p],
-    "thn_gemm_smallm_supported": [c_int, c_int, c_int],
     "thn_gemm_tcgen05_supported": [c_int, c_int, c_int],
     "thn_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_stream_supported": [c_int, c_int, c_int],
     "thn_gemm_stream_scratch": [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_void_p],
-    "thn_gemm_smallm_plan": [c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "thn_gemm_smallm_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                             c_int, c_void_p],
     "thn_step_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_advance": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -90,9 +86,6 @@ def lib():
         loaded.thn_set_pdl.argtypes = [c_int]
         loaded.thn_set_pdl.restype = None
         loaded.thn_set_pdl(0 if os.environ.get("THN_PDL", "1").strip().lower() in ("0", "false", "no", "off") else 1)
-        loaded.thn_set_weight_prefetch.argtypes = [c_int]
-        loaded.thn_set_weight_prefetch.restype = None
-        loaded.thn_set_weight_prefetch(0 if os.environ.get("THN_PREFETCH", "1").strip() in ("0", "false", "off") else 1)
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -313,60 +306,31 @@ def _sm_count_of(device) -> int:
     return _sm_count[index]
 
 
-# Few-row products go to this library's weight-streaming kernel when the reduction is at
-# least this deep; measured on B200 at 8 rows (kernel_bench.py): it beats the vendor library
-# at K = 4096 and 9728 (9.9 vs 10.3 us, 15.0 vs 20.0 us) and loses at K = 2560 (10.9 vs 7.5 us,
-# 21.9 vs 17.5 us).
-SMALLM_MIN_K = int(os.environ.get("THN_SMALLM_MIN_K", 4096))
+# Products with at most this many rows go to this library's weight-streaming kernel when the
+# reduction is at least STREAM_MIN_K deep or the weight has at least STREAM_MIN_N rows;
+# measured on B200 at 8 rows (kernel_bench.py): it beats the vendor library at K = 4096 and
+# 9728 and on the head (9.3 vs 10.3 us, 14.1 vs 20.4 us, 119 vs 127 us) and loses at K = 2560
+# (10.4 vs 7.5 us, 20.0 vs 17.5 us) and beyond 16 rows.
+STREAM_MAX_ROWS = 16
+STREAM_MIN_K = int(os.environ.get("THN_STREAM_MIN_K", 4096))
+STREAM_MIN_N = 65536
+STREAM_POLICY = os.environ.get("THN_LINEAR_STREAM", "auto")     # auto | all | none (measurement)
 
-_smallm_plans = {}
-_smallm_counters = {}
-
-
-def smallm_plan(m: int, n: int, k: int, device, n_warps: int = 0):
-    """(span, slabs) of the weight-streaming product for a shape; cached."""
-    key = (m <= 8, n, k, n_warps, torch.device(device).index or 0)
-    if key not in _smallm_plans:
-        span = ctypes.c_int(0)
-        slabs = lib().thn_gemm_smallm_plan(m, n, k, _sm_count_of(device), n_warps, ctypes.byref(span))
-        _smallm_plans[key] = (span.value, slabs)
-    return _smallm_plans[key]
+_device_counters = {}
 
 
-def _smallm_counter_buffer(n_tiles: int, device) -> torch.Tensor:
-    """Arrival counters, one per 16 weight rows; zero between calls (the kernel resets them)."""
+def _counter_buffer(n: int, device) -> torch.Tensor:
+    """Arrival counters for kernels whose last-arriving block finishes a shared result; zero
+    between calls (the kernels reset them)."""
     index = torch.device(device).index or 0
-    have = _smallm_counters.get(index)
-    if have is None or have.numel() < n_tiles:
-        have = torch.zeros(max(n_tiles, 1 << 20), dtype=torch.int32, device=device)   # never regrown in practice: graphs keep its address
-        _smallm_counters[index] = have
+    have = _device_counters.get(index)
+    if have is None or have.numel() < n:
+        have = torch.zeros(max(n, 1 << 20), dtype=torch.int32, device=device)   # never regrown in practice: graphs keep its address
+        _device_counters[index] = have
     return have
 
 
-def linear_smallm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                  n_warps: int = 0, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """The weight-streaming product for few rows (bfloat16 operands, M <= 16, K a multiple of
-    64) -> ``[M, N]`` in bfloat16 or float32.  Tiles shared by several warps go through
-    float32 scratch memory, allocated here unless given.  ``n_warps`` overrides the number
-    of warps the work is cut for (tests)."""
-    _need(x, "linear_smallm x", torch.bfloat16)
-    _need(weight, "linear_smallm weight", torch.bfloat16)
-    m, k = x.shape
-    n = weight.shape[0]
-    span, slabs = smallm_plan(m, n, k, x.device, n_warps)
-    if slabs and scratch is None:
-        scratch = torch.empty(slabs * m * n, dtype=torch.float32, device=x.device)
-    if slabs and scratch.numel() < slabs * m * n:
-        raise KernelError(f"linear_smallm: scratch has {scratch.numel()} floats, {slabs * m * n} needed")
-    counters = _smallm_counter_buffer((n + 15) // 16, x.device) if slabs else None
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    _call("thn_gemm_smallm_bf16", _ptr(out), DTYPE_CODE[out_dtype], _ptr(scratch) if slabs else None, _ptr(counters),
-          _ptr(x), _ptr(weight), m, n, k, span, slabs, _stream())
-    return out
-
-
 _stream_needs = {}
-_stream_counters = {}
 
 
 def _stream_need(m: int, n: int, k: int, swiglu: bool, n_blocks: int):
@@ -383,8 +347,8 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     """The TMA / tcgen05 weight-streaming product for steps of at most 64 rows (bfloat16
     operands, K a multiple of 8) -> ``[M, N]`` in bfloat16 or float32.  With ``swiglu`` the
     weight is ``[2 * I, K]`` (gate rows, then up rows) and the result is ``silu(gate) * up``,
-    ``[M, I]``, in one kernel.  ``n_blocks`` overrides the number of blocks the work is cut
-    for (tests; default: one per SM)."""
+    ``[M, I]``, in one kernel.  ``n_blocks`` overrides how the work is cut (tests): that many
+    blocks with balanced runs, or, negative, one thread-block cluster of that size per tile."""
     _need(x, "linear_stream x", torch.bfloat16)
     _need(weight, "linear_stream weight", torch.bfloat16)
     m, k = x.shape
@@ -392,11 +356,7 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype 
     if weight.shape[1] != k or (swiglu and weight.shape[0] % 2):
         raise KernelError(f"linear_stream: shapes x {tuple(x.shape)}, weight {tuple(weight.shape)}")
     floats, n_counters = _stream_need(m, n, k, swiglu, n_blocks)
-    index = x.device.index or 0
-    counters = _stream_counters.get(index)
-    if counters is None or counters.numel() < n_counters:
-        counters = torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device=x.device)   # graphs keep its address
-        _stream_counters[index] = counters
+    counters = _counter_buffer(n_counters, x.device)
     scratch = torch.empty(floats, dtype=torch.float32, device=x.device)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     _call("thn_gemm_stream_bf16", _ptr(out), DTYPE_CODE[out_dtype], _ptr(scratch), _ptr(counters), _ptr(x),
@@ -420,19 +380,12 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, err: Optional[torch.Te
     return out
 
 
-STREAM_POLICY = os.environ.get("THN_LINEAR_STREAM", "auto")
-
-
 def _stream_takes(m: int, n: int, k: int, fused: bool = False) -> bool:
-    if not lib().thn_gemm_stream_supported(m, n, k):
+    if STREAM_POLICY == "none" or not lib().thn_gemm_stream_supported(m, n, k):
         return False
-    if STREAM_POLICY in ("all", "none"):
-        return STREAM_POLICY == "all"
-    if STREAM_POLICY == "deep":
-        return k >= SMALLM_MIN_K or n >= 65536
-    if STREAM_POLICY == "fused":
-        return fused or k >= SMALLM_MIN_K or n >= 65536
-    return False
+    if STREAM_POLICY == "all":
+        return True
+    return not fused and m <= STREAM_MAX_ROWS and (k >= STREAM_MIN_K or n >= STREAM_MIN_N)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -440,17 +393,17 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, err: Optional[torch.
     weight-streaming product takes the shape, else the product followed by the activation."""
     if x.dtype == torch.bfloat16 and _stream_takes(x.shape[0], w_gate_up.shape[0] // 2, x.shape[1], fused=True):
         return linear_stream(x, w_gate_up, swiglu=True, err=err)
-    return swiglu(linear(x, w_gate_up, split_ok=True, err=err))
+    return swiglu(linear(x, w_gate_up, err=err))
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False,
-           err: Optional[torch.Tensor] = None):
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           err: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] @ weight[N, K]^T.  float32: this library's FFMA kernel.  bfloat16 with few
-    rows: this library's weight-streaming kernel.  bfloat16 otherwise: the vendor library's
-    tensor-core product with float32 accumulation (the reference's choice,
+    rows and a deep reduction or a tall weight: this library's weight-streaming kernel
+    (``err``: the step's device error word for its bounded waits).  bfloat16 otherwise: the
+    vendor library's tensor-core product with float32 accumulation (the reference's choice,
     engine/engine.py:341-350).  ``out_dtype=torch.float32`` keeps the accumulator's
-    precision (used for logits).  With ``split_ok`` the result may be a :class:`SplitSum`
-    for a consuming kernel to add up; otherwise it is always a tensor."""
+    precision (used for logits)."""
     _need(x, "linear x")
     _need(weight, "linear weight", x.dtype)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
@@ -463,8 +416,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         raise KernelError(f"linear: dtype {x.dtype} is not supported")
     if _stream_takes(x.shape[0], weight.shape[0], x.shape[1]):
         return linear_stream(x, weight, out_dtype or torch.bfloat16, err=err)
-    if x.shape[1] >= SMALLM_MIN_K and lib().thn_gemm_smallm_supported(x.shape[0], weight.shape[0], x.shape[1]):
-        return linear_smallm(x, weight, out_dtype or torch.bfloat16)
     if out_dtype in (None, torch.bfloat16):
         return torch.nn.functional.linear(x, weight)
     return torch.mm(x, weight.t(), out_dtype=out_dtype)
@@ -591,7 +542,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if need and scratch.numel() < need:
         raise KernelError(f"attention_decode: scratch has {scratch.numel()} floats, {need} needed")
-    counters = _smallm_counter_buffer(n_seqs * kv.n_kv, q.device) if n_splits > 1 and fused_merge else None
+    counters = _counter_buffer(n_seqs * kv.n_kv, q.device) if n_splits > 1 and fused_merge else None
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
@@ -640,7 +591,7 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 
 __all__ = [
-    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_smallm", "linear_tcgen05", "resolve", "smallm_plan", "add_rmsnorm", "advance",
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_stream", "linear_swiglu", "linear_tcgen05", "resolve", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

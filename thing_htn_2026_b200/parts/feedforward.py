@@ -30,4 +30,4 @@ class SwiGLU:
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         err = getattr(ctx, "err", None)
-        return ops.linear(ops.linear_swiglu(x, self.w_gate_up, err), self.w_down, split_ok=True, err=err)
+        return ops.linear(ops.linear_swiglu(x, self.w_gate_up, err), self.w_down, err=err)
