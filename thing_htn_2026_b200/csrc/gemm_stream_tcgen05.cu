@@ -388,10 +388,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
 
 // Few tiles (N small against the number of SMs): every tile is cut along K among the blocks
 // of one thread-block cluster, one tile per cluster, and the partial sums meet in distributed
-// shared memory instead of global memory: each block parks its partial in its own shared
-// memory, the cluster's hardware barrier orders it, and block q of the cluster adds, in
-// ascending k order, the columns j = q, q + cluster size, ... of every block's partial and
-// stores them.  The second barrier keeps every block's shared memory alive until all have read.
+// shared memory instead of global memory: block q of the cluster owns the columns j = q,
+// q + cluster size, ...; every block writes its partial of a column into the owner's shared
+// memory (a region of its own, beside the stages, since the owner may still be streaming),
+// the cluster's hardware barrier orders it, and the owner adds the partials in ascending k
+// order and stores.  After the barrier nobody touches another block's memory, so a block
+// may leave as soon as it has stored.
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -406,28 +408,40 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
-__device__ __forceinline__ float load_from_block(const float* mine, uint32_t rank) {
+// *mine as it lies in block `rank` of the cluster <- v
+__device__ __forceinline__ void store_to_block(float* mine, uint32_t rank, float v) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(mine)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
+
+// Stages of the cluster kernel: the shared-memory budget less the region that receives the
+// other blocks' partials, [own column][sending block][row], at most NX + 8 x 128 floats.
+template <int NX>
+struct ClusterShape {
+    static constexpr int kRecvFloats = (NX + 8) * BW;
+    static constexpr int kStages =
+        (int)((kSmemBudget - kRecvFloats * 4) / Shape<NX, 0>::kStageBytes) < kMaxStages
+            ? (int)((kSmemBudget - kRecvFloats * 4) / Shape<NX, 0>::kStageBytes) : kMaxStages;
+    static constexpr size_t kSmemBytes =
+        (size_t)kStages * Shape<NX, 0>::kStageBytes + kRecvFloats * 4 + 1024 /* alignment */ + 512 /* barriers */;
+};
 
 template <int NX, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, OutT* __restrict__ out,
     int M, int N, int chunks, int* __restrict__ err) {
     using S = Shape<NX, 0>;
+    constexpr int kStages = ClusterShape<NX>::kStages;
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)S::kStages * S::kStageBytes);
-    uint64_t* empty = full + S::kStages;
-    uint64_t* acc_full = empty + S::kStages;
+    float* recv = reinterpret_cast<float*>(tiles + (size_t)kStages * S::kStageBytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(recv + ClusterShape<NX>::kRecvFloats);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* partial = reinterpret_cast<float*>(tiles);      // [column][row of the tile], over the drained stages
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)cluster_rank(), n_ranks = (int)cluster_size();
@@ -435,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
     const int c0 = (int)((long long)chunks * rank / n_ranks), c1 = (int)((long long)chunks * (rank + 1) / n_ranks);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S::kStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(full + s, 1);
             mbar_init(empty + s, 1);
         }
@@ -464,14 +478,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
         auto load_x = [&](int s, int c) {
             tma_load_2d(tiles + (size_t)s * S::kStageBytes + kWBytes, &map_x, full + s, c * BK, 0);
         };
-        const int early = min(S::kStages, c1 - c0);
+        const int early = min(kStages, c1 - c0);
         for (int i = 0; i < early; ++i) load_w(i, c0 + i);
         pdl_wait();
         for (int i = 0; i < early; ++i) load_x(i, c0 + i);
         int it = early;
         for (int c = c0 + early; c < c1 && !*give_up; ++c, ++it) {
-            const int s = it % S::kStages;
-            if (!mbar_wait(empty + s, ((it / S::kStages) & 1) ^ 1)) {
+            const int s = it % kStages;
+            if (!mbar_wait(empty + s, ((it / kStages) & 1) ^ 1)) {
                 if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 *give_up = 1;
                 break;
@@ -484,8 +498,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
         bool ok = true;
         int it = 0;
         for (int c = c0; c < c1 && ok && !*give_up; ++c, ++it) {
-            const int s = it % S::kStages;
-            ok = mbar_wait(full + s, (it / S::kStages) & 1);
+            const int s = it % kStages;
+            ok = mbar_wait(full + s, (it / kStages) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t w_addr = smem_addr(tiles + (size_t)s * S::kStageBytes);
@@ -501,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
             *give_up = 1;
         }
     } else if (warp >= 2) {
-        // ---- epilogue, first half: this block's partial into its shared memory
+        // ---- epilogue, first half: this block's partial, column by column, to the columns' owners
         pdl_wait();
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
@@ -520,23 +534,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
                 *give_up = 1;
             }
         }
-        // every product has been committed, so no stage is being read or written any more
+        // column j goes to block j % n_ranks, as that block's column j / n_ranks, sender `rank`
 #pragma unroll
         for (int j = 0; j < NX; ++j)
-            if (j < M) partial[j * BW + r] = acc[j];
+            if (j < M) store_to_block(recv + ((j / n_ranks) * n_ranks + rank) * BW + r, (uint32_t)(j % n_ranks), acc[j]);
     }
     cluster_sync();
     if (warp >= 2) {
-        // ---- epilogue, second half: this block's share of the columns, summed over the cluster
+        // ---- epilogue, second half: this block's columns, partials added in ascending k order
         const int r = (warp & 3) * 32 + lane;
         const int n = tile * BW + r;
-        for (int j = rank; j < M; j += n_ranks) {
+        for (int j = rank, jl = 0; j < M; j += n_ranks, ++jl) {
+            float v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = q < n_ranks ? recv[(jl * n_ranks + q) * BW + r] : 0.f;
             float sum = 0.f;
-            for (int q = 0; q < n_ranks; ++q) sum += load_from_block(partial + j * BW + r, (uint32_t)q);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) sum += v[q];
             if (n < N) out[(size_t)j * N + n] = from_f32<OutT>(sum);
         }
     }
-    cluster_sync();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -632,7 +649,7 @@ int cluster_size_for(int n_tiles) {
     if (resident[0] < 0) {
         resident[0] = 0;
         if (cudaFuncSetAttribute(gemm_stream_cluster_kernel<NX, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)S::kSmemBytes) != cudaSuccess) {
+                                 (int)ClusterShape<NX>::kSmemBytes) != cudaSuccess) {
             cudaGetLastError();
             for (int c = 1; c <= 8; ++c) resident[c] = 0;
         }
@@ -642,7 +659,7 @@ int cluster_size_for(int n_tiles) {
             cudaLaunchConfig_t config = {};
             config.gridDim = dim3((unsigned)(c * 64));
             config.blockDim = dim3(kThreads);
-            config.dynamicSmemBytes = S::kSmemBytes;
+            config.dynamicSmemBytes = ClusterShape<NX>::kSmemBytes;
             cudaLaunchAttribute attribute[1];
             attribute[0].id = cudaLaunchAttributeClusterDimension;
             attribute[0].val.clusterDim.x = (unsigned)c;
@@ -669,7 +686,7 @@ int launch_cluster(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)(n_tiles * c));
     config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = S::kSmemBytes;
+    config.dynamicSmemBytes = ClusterShape<NX>::kSmemBytes;
     config.stream = stream;
     cudaLaunchAttribute attribute[2];
     attribute[0].id = cudaLaunchAttributeClusterDimension;
