@@ -384,7 +384,7 @@ def _stream_takes(m: int, n: int, k: int, fused: bool = False) -> bool:
     if STREAM_POLICY == "none" or not lib().thn_gemm_stream_supported(m, n, k):
         return False
     if STREAM_POLICY == "all":
-        return not fused or os.environ.get("THN_STREAM_FUSED", "1") == "1"
+        return True
     return not fused and m <= STREAM_MAX_ROWS and (k >= STREAM_MIN_K or n >= STREAM_MIN_N)
 
 
