@@ -402,6 +402,61 @@ def test_attention_window_edge(kernel, dtype):
     close(got, want, dtype, "window edge", scale=4)
 
 
+# ----------------------------------------------------------------------------- fused single-token step
+
+
+@pytest.mark.parametrize("gain_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n_q,n_kv,D,window", [(8, 2, 128, None), (6, 6, 64, None), (16, 1, 128, 100), (32, 8, 128, None)])
+def test_qkv_attention_fused_decode_equals_two_kernels(n_q, n_kv, D, window, gain_dtype):
+    """A single-token step through the one fused kernel (q/k norm, rotation, cache write,
+    attention) gives, bit for bit, the output and the cache of the two separate kernels.
+    The lengths put the new token at a page's first row, at its last row and in the middle,
+    and make one sequence one token long."""
+    from thing_htn_2026_b200.config.base import PartSpec
+    from thing_htn_2026_b200.parts import Runtime, part_class
+    o = ops()
+    dtype = torch.bfloat16
+    lengths = [129, 64, 1, 300, 77, 640]
+    old = [n - 1 for n in lengths]
+    fix = PagedFixture(n_kv, D, lengths, dtype, window)
+    # the tokens before this step
+    keep = fix.slots
+    fix.slots = [s for s, n in zip(keep, old) if n]
+    rows, cu = fix.rows([n for n in old if n])
+    k = rand((cu[-1], n_kv, D), dtype, 70)
+    v = rand((cu[-1], n_kv, D), dtype, 71)
+    write_kv(fix, rows, k, v, n_q)
+    fix.advance(rows, [n for n in old if n])
+    fix.slots = keep
+
+    rope = part_class("position", "rope")(PartSpec("rope", {"head_dim": D, "theta": 54321.0}),
+                                          Runtime(dtype, torch.device(DEV), {}))
+    rope.ensure(1024)
+    rows, cu = fix.rows([1] * len(lengths))
+    qkv = rand((len(lengths), (n_q + 2 * n_kv) * D), dtype, 72, 2.0).to(DEV)
+    qg = (1 + 0.3 * torch.randn(D, generator=torch.Generator().manual_seed(73))).to(gain_dtype).to(DEV)
+    kg = (1 + 0.3 * torch.randn(D, generator=torch.Generator().manual_seed(74))).to(gain_dtype).to(DEV)
+    err = o.new_error_word(DEV)
+    before = fix.kv.storage.clone()
+    scale = D ** -0.5
+
+    q = o.qk_norm_rope_cache(qkv, qg, kg, 1e-6, rope.tables(), rows, fix.kv, n_q, True, err)
+    want = o.attention(q, rows, fix.kv, n_q, scale, window, err)
+    cache_want = fix.kv.storage.clone()
+    assert not torch.equal(cache_want, before)
+
+    fix.kv.storage.copy_(before)
+    got = o.qkv_attention(qkv, qg, kg, 1e-6, rope.tables(), rows, fix.kv, n_q, scale, window, True, err)
+    assert int(err.item()) == 0
+    assert torch.equal(fix.kv.storage, cache_want), "the fused kernel leaves another cache"
+    assert torch.equal(got, want), "the fused kernel gives another output"
+
+    # a layer that reads another layer's cache: the token is there already, nothing is written
+    got = o.qkv_attention(qkv, qg, kg, 1e-6, rope.tables(), rows, fix.kv, n_q, scale, window, False, err)
+    assert torch.equal(got, want) and torch.equal(fix.kv.storage, cache_want)
+    assert int(err.item()) == 0
+
+
 # ----------------------------------------------------------------------------- q/k norm, rotation, cache write
 
 

@@ -280,12 +280,60 @@ __global__ void __launch_bounds__(kPrefillThreads) attention_prefill_kernel(
 // output; nobody waits.  Without counters the merge kernel does it.
 // STAGES: tile buffers (2 when a block has few tiles and more blocks per SM matter, 3 when
 // one block walks a whole sequence).
-template <int D, int STAGES>
+//
+// FUSED: q is not given; the block takes the step's raw q/k/v rows (the output of the fused
+// q/k/v product) and does what the separate kernel of rope_cache.cu does, with the same
+// arithmetic (engine/kernels/torch_ref.py:47-58 and :100-117): its query heads are
+// normalised and rotated on the way into shared memory, and the block whose keys end with the
+// sequence's new position normalises and rotates the new key, copies the new value, writes
+// both to the cache and into its own tile.  One kernel less per layer and step.
+struct FusedInput {
+    const __nv_bfloat16* qkv;    // [n_seqs, (n_q + 2 n_kv) * D]
+    const void* q_gain;          // [D] bfloat16, or float32 when gain_f32
+    const void* k_gain;
+    const float* cos_tab;        // [table_len, D / 2]
+    const float* sin_tab;
+    float eps;
+    int table_len, gain_f32, write_cache;
+};
+
+__device__ __forceinline__ float gain_at(const void* gain, int f32, int i) {
+    return f32 ? reinterpret_cast<const float*>(gain)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(gain)[i]);
+}
+
+// One head of D values, a lane holding [d0, d0 + E) and [D/2 + d0, ..): RMSNorm with gain,
+// then the rotation by the row's angles; every product rounded to bfloat16 as the reference does.
+template <int D>
+__device__ __forceinline__ void norm_rotate_head(const __nv_bfloat16* __restrict__ src, const void* gain, int gain_f32,
+                                                 float eps, const float (&c)[D / 64], const float (&sn)[D / 64], int lane,
+                                                 __nv_bfloat16 (&lo)[D / 64], __nv_bfloat16 (&hi)[D / 64]) {
+    using B = __nv_bfloat16;
+    constexpr int E = D / 64, kHalf = D / 2;
+    const int d0 = lane * E;
+    float a[E], b[E], ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        a[e] = __bfloat162float(src[d0 + e]);
+        b[e] = __bfloat162float(src[kHalf + d0 + e]);
+        ss += a[e] * a[e] + b[e] * b[e];
+    }
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const float x0 = rnd<B>(gain_at(gain, gain_f32, d0 + e) * rnd<B>(a[e] * rstd));
+        const float x1 = rnd<B>(gain_at(gain, gain_f32, kHalf + d0 + e) * rnd<B>(b[e] * rstd));
+        lo[e] = __float2bfloat16_rn(rnd<B>(x0 * c[e]) + rnd<B>(-x1 * sn[e]));
+        hi[e] = __float2bfloat16_rn(rnd<B>(x1 * c[e]) + rnd<B>(x0 * sn[e]));
+    }
+}
+
+template <int D, int STAGES, bool FUSED>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
     PagedKV kv, int n_q, int n_splits, float scale_log2, int window, int* __restrict__ counters,
-    int* __restrict__ err) {
+    int* __restrict__ err, FusedInput fused) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int kPitch = D + 8, kStages = STAGES;
@@ -309,12 +357,17 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     const int t_begin = t_first + split * per_split;
     const int t_end = min(t_begin + per_split, t_last + 1);      // exclusive; may be <= t_begin (empty split)
 
-    for (int c = threadIdx.x; c < 16 * (D / 8); c += kThreads) {
-        const int r = c / (D / 8), col = (c % (D / 8)) * 8;
-        if (r < G)
-            cp_async16(q_smem + r * kPitch + col, q + ((size_t)b * n_q + kvh * G + r) * D + col);
-        else
-            *reinterpret_cast<uint4*>(q_smem + r * kPitch + col) = make_uint4(0, 0, 0, 0);
+    constexpr int E = D / 64, kHalf = D / 2;
+    __nv_bfloat16 new_k_lo[E], new_k_hi[E], new_v_lo[E], new_v_hi[E];      // warp 0, FUSED: the step's own key and value
+    const bool patches = FUSED && fused.write_cache && t_begin <= t_last && t_last < t_end;
+    if (!FUSED) {
+        for (int c = threadIdx.x; c < 16 * (D / 8); c += kThreads) {
+            const int r = c / (D / 8), col = (c % (D / 8)) * 8;
+            if (r < G)
+                cp_async16(q_smem + r * kPitch + col, q + ((size_t)b * n_q + kvh * G + r) * D + col);
+            else
+                *reinterpret_cast<uint4*>(q_smem + r * kPitch + col) = make_uint4(0, 0, 0, 0);
+        }
     }
     cp_async_commit();
 
@@ -334,6 +387,47 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     issue(t_begin, 0);
     if (kStages == 3) issue(t_begin + 1, 1);
 
+    // the first tiles are on their way while the block prepares its queries
+    if (FUSED) {
+        if (pos >= fused.table_len) {
+            if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+            cp_async_wait<0>();
+            return;
+        }
+        const int d0 = lane * E;
+        float c[E], sn[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            c[e] = rnd<__nv_bfloat16>(fused.cos_tab[(size_t)pos * kHalf + d0 + e]);
+            sn[e] = rnd<__nv_bfloat16>(fused.sin_tab[(size_t)pos * kHalf + d0 + e]);
+        }
+        const __nv_bfloat16* row = fused.qkv + (size_t)b * (n_q + 2 * kv.n_kv) * D;
+        for (int r = warp; r < 16; r += kThreads / 32) {
+            __nv_bfloat16 lo[E], hi[E];
+            if (r < G) {
+                norm_rotate_head<D>(row + (size_t)(kvh * G + r) * D, fused.q_gain, fused.gain_f32, fused.eps, c, sn, lane,
+                                    lo, hi);
+            } else {
+#pragma unroll
+                for (int e = 0; e < E; ++e) lo[e] = hi[e] = __float2bfloat16_rn(0.f);
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                q_smem[r * kPitch + d0 + e] = lo[e];
+                q_smem[r * kPitch + kHalf + d0 + e] = hi[e];
+            }
+        }
+        if (patches && warp == 0) {
+            norm_rotate_head<D>(row + (size_t)(n_q + kvh) * D, fused.k_gain, fused.gain_f32, fused.eps, c, sn, lane,
+                                new_k_lo, new_k_hi);
+            const __nv_bfloat16* v_row = row + (size_t)(n_q + kv.n_kv + kvh) * D;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                new_v_lo[e] = v_row[d0 + e];
+                new_v_hi[e] = v_row[kHalf + d0 + e];
+            }
+        }
+    }
     if (kStages == 3) cp_async_wait<2>(); else cp_async_wait<1>();          // Q has landed
     __syncthreads();
     uint32_t qf[D / 16][4];
@@ -360,6 +454,26 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             cp_async_wait<1>();
         }
         __syncthreads();
+        if (FUSED && patches && t == t_last) {
+            // the tile came from the cache without this step's token: put it in, here and there
+            if (warp == 0) {
+                const int page = pages[t], in_page = pos % kTile, d0 = lane * E;
+                if (page >= 0) {
+                    __nv_bfloat16* k_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 0, kvh, in_page);
+                    __nv_bfloat16* v_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 1, kvh, in_page);
+                    __nv_bfloat16* k_row = k_smem + stage * kTile * kPitch + in_page * kPitch;
+                    __nv_bfloat16* v_row = v_smem + stage * kTile * kPitch + in_page * kPitch;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        k_dst[d0 + e] = k_row[d0 + e] = new_k_lo[e];
+                        k_dst[kHalf + d0 + e] = k_row[kHalf + d0 + e] = new_k_hi[e];
+                        v_dst[d0 + e] = v_row[d0 + e] = new_v_lo[e];
+                        v_dst[kHalf + d0 + e] = v_row[kHalf + d0 + e] = new_v_hi[e];
+                    }
+                }
+            }
+            __syncthreads();
+        }
         const int key0 = t * kTile + warp * 16;
         float s[2][4];
         qk_tile<D, 2>(s, qf, k_smem + stage * kTile * kPitch, warp * 2, lane);
@@ -512,11 +626,11 @@ int launch_prefill(void* out, const void* q, const int* tile_row0, const int* ti
     return thn_launch_status("attention_prefill");
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool FUSED>
 int configure_decode() {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, FUSED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)decode_smem<D, STAGES>());
         if (e != cudaSuccess) {
@@ -531,28 +645,28 @@ int configure_decode() {
 
 template <int D>
 int decode_blocks_per_sm() {
-    if (configure_decode<D, 2>() != THN_OK) return 1;
+    if (configure_decode<D, 2, false>() != THN_OK) return 1;
     int blocks = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2>, kThreads,
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2, false>, kThreads,
                                                                   decode_smem<D, 2>());
     return (e == cudaSuccess && blocks > 0) ? blocks : 1;
 }
 
-template <int D>
+template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
-                  cudaStream_t stream) {
-    int configured = n_splits == 1 ? configure_decode<D, 3>() : configure_decode<D, 2>();
+                  cudaStream_t stream, FusedInput fused = FusedInput{}) {
+    int configured = n_splits == 1 ? configure_decode<D, 3, FUSED>() : configure_decode<D, 2, FUSED>();
     if (configured != THN_OK) return configured;
     dim3 grid(n_seqs, kv.n_kv, n_splits);
     if (n_splits == 1)
-        thn_launch(attention_decode_kernel<D, 3>, grid, kThreads, decode_smem<D, 3>(), stream, (__nv_bfloat16*)out,
-                   part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits, scale * kLog2e,
-                   window, counters, err);
+        thn_launch(attention_decode_kernel<D, 3, FUSED>, grid, kThreads, decode_smem<D, 3>(), stream,
+                   (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
+                   scale * kLog2e, window, counters, err, fused);
     else
-        thn_launch(attention_decode_kernel<D, 2>, grid, kThreads, decode_smem<D, 2>(), stream, (__nv_bfloat16*)out,
-                   part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits, scale * kLog2e,
-                   window, counters, err);
+        thn_launch(attention_decode_kernel<D, 2, FUSED>, grid, kThreads, decode_smem<D, 2>(), stream,
+                   (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
+                   scale * kLog2e, window, counters, err, fused);
     int status = thn_launch_status("attention_decode");
     if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
     thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
@@ -624,6 +738,39 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     if (head_dim == 64)
         return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
     return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
+}
+
+// The same with the q/k norm, the rotation and the cache write of the step's token inside the
+// kernel: qkv [n_seqs, (n_q + 2 n_kv) * head_dim] bfloat16 is the raw output of the q/k/v
+// product; gains [head_dim] bfloat16 (w_dtype THN_BF16) or float32; cos/sin [table_len,
+// head_dim / 2].  With write_cache == 0 the cache already holds the step's token (a layer that
+// reads another layer's cache) and only q is prepared.
+THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const void* q_gain, const void* k_gain,
+                                            int w_dtype, float eps, const float* cos_tab, const float* sin_tab,
+                                            int table_len, int write_cache, const int* row_slot, const int* row_pos,
+                                            void* kv_base, const int* block_table, int bt_stride, int n_kv,
+                                            int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
+                                            int window, float* scratch, int* counters, int* err, cudaStream_t stream) {
+    THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode_fused: bad sizes");
+    THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode_fused: at most 32 splits with counters, got %d",
+                  n_splits);
+    THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
+                       "attention_decode_fused: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
+                       head_dim, page_size, n_q, n_kv);
+    THN_CHECK_ARG(qkv && q_gain && k_gain && cos_tab && sin_tab, "attention_decode_fused: gains and angles, please");
+    THN_CHECK_ARG(w_dtype == THN_BF16 || w_dtype == THN_F32, "attention_decode_fused: unknown gain dtype %d", w_dtype);
+    THN_CHECK_ARG(n_splits == 1 || scratch != nullptr, "attention_decode_fused: %d splits need scratch memory", n_splits);
+    if (n_seqs == 0) return THN_OK;
+    PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
+    FusedInput fused{(const __nv_bfloat16*)qkv, q_gain, k_gain, cos_tab, sin_tab, eps, table_len, w_dtype == THN_F32,
+                     write_cache};
+    if (head_dim == 64)
+        return launch_decode<64, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
+                                       window, counters, err, stream, fused);
+    return launch_decode<128, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
+                                    window, counters, err, stream, fused);
 }
 
 // ------------------------------------------------------------------ no device allocation

@@ -52,6 +52,9 @@ _SIGNATURES = {
     "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_void_p, c_void_p],
+    "thn_attention_decode_fused_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+                                        c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -550,6 +553,40 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     return out
 
 
+FUSE_DECODE_ATTENTION = os.environ.get("THN_FUSE_DECODE", "1").strip().lower() not in ("0", "false", "no", "off")
+
+
+def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                  rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int, scale: float,
+                  window: Optional[int], write_cache: bool, err: torch.Tensor) -> torch.Tensor:
+    """From the raw q/k/v rows of a step to the attention output: per-head q/k norm, rotation,
+    cache write and attention over the cache.  One kernel for single-token steps in bfloat16
+    with head norm and full rotation at the tensor-core kernel's sizes; otherwise
+    :func:`qk_norm_rope_cache` followed by :func:`attention`."""
+    fusable = (FUSE_DECODE_ATTENTION and rows.max_q_len == 1 and isinstance(qkv, torch.Tensor)
+               and qkv.dtype == torch.bfloat16 and q_gain is not None and k_gain is not None and rotary is not None
+               and rotary.rotary_dim == kv.head_dim and kv.storage.dtype == torch.bfloat16
+               and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv))
+    if not fusable:
+        q = qk_norm_rope_cache(qkv, q_gain, k_gain, eps, rotary, rows, kv, n_q, write_cache, err)
+        return attention(q, rows, kv, n_q, scale, window, err)
+    n_seqs = rows.n_rows
+    width = (n_q + 2 * kv.n_kv) * kv.head_dim
+    if tuple(qkv.shape) != (n_seqs, width):
+        raise KernelError(f"qkv_attention: qkv is {tuple(qkv.shape)}, expected {(n_seqs, width)}")
+    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim)
+    need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
+    scratch = torch.empty(need, dtype=torch.float32, device=qkv.device) if need else None
+    counters = _counter_buffer(n_seqs * kv.n_kv, qkv.device) if n_splits > 1 else None
+    out = torch.empty((n_seqs, n_q * kv.head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _call("thn_attention_decode_fused_bf16", _ptr(out), _ptr(qkv), _ptr(q_gain), _ptr(k_gain),
+          _code(q_gain, "qk gains"), float(eps), _ptr(rotary.cos), _ptr(rotary.sin), rotary.cos.shape[0],
+          int(bool(write_cache)), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
+          kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_seqs, n_q, n_splits, float(scale),
+          int(window or 0), _ptr(scratch), _ptr(counters), _ptr(err), _stream())
+    return out
+
+
 # ------------------------------------------------------------------ token choice
 
 
@@ -593,5 +630,5 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 __all__ = [
     "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_stream", "linear_swiglu", "linear_tcgen05", "resolve", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
-    "qk_norm_rope_cache", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
+    "qk_norm_rope_cache", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -67,8 +67,7 @@ class Attention:
     def forward(self, x: torch.Tensor, ctx: StepContext, entry: ScheduleEntry) -> torch.Tensor:
         kv = ctx.cache.kv_view(entry.cache)
         qkv = ops.linear(x, self.w_qkv, err=ctx.err)
-        q = ops.qk_norm_rope_cache(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
-                                   self.position.tables() if self.position is not None else None,
-                                   ctx.rows, kv, self.n_q, entry.writes_cache, ctx.err)
-        a = ops.attention(q, ctx.rows, kv, self.n_q, self.scale, self.window, ctx.err)
+        a = ops.qkv_attention(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
+                              self.position.tables() if self.position is not None else None,
+                              ctx.rows, kv, self.n_q, self.scale, self.window, entry.writes_cache, ctx.err)
         return ops.linear(a, self.w_o, err=ctx.err)
