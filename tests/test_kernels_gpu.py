@@ -336,10 +336,12 @@ def test_attention_prefill_tcgen05(n_q, n_kv, window):
     close(got, want, dtype, "tcgen05 attention, continued prompts")
 
 
-@pytest.mark.parametrize("splits", ["", "1", "3", "8"])
+@pytest.mark.parametrize("splits", ["", "1", "3", "8", "12"])
 @pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 64, None), (32, 8, 128, None), (6, 3, 64, 70), (3, 1, 128, 24),
                                                (16, 1, 64, None), (5, 5, 128, 200)])
 def test_attention_decode_tensor_cores(n_q, n_kv, D, window, splits):
+    """One block per sequence (1), splits that meet in a thread-block cluster's shared memory
+    (3, 8) and splits that meet in global memory (12: more than a cluster holds)."""
     dtype = torch.bfloat16
     lengths = [700, 64, 65, 1, 333, 128]
     got, want = attention_case("decode" + splits, dtype, n_q, n_kv, D, lengths, [1] * len(lengths), window)

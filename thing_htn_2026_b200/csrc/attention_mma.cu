@@ -328,7 +328,24 @@ __device__ __forceinline__ void norm_rotate_head(const __nv_bfloat16* __restrict
     }
 }
 
-template <int D, int STAGES, bool FUSED>
+// CLUSTER: the splits of one (sequence, kv head) are the blocks of one thread-block cluster,
+// and their partial results meet in distributed shared memory instead of global memory:
+// every block parks its partial in its own shared memory, the cluster's hardware barrier
+// orders it, block 0 reads all of them, combines them in split order and writes the output;
+// a second barrier keeps every block's shared memory alive until block 0 has read it.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float load_from_block(const float* mine, uint32_t rank) {
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(mine), remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
+    return v;
+}
+
+template <int D, int STAGES, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const __nv_bfloat16* __restrict__ q, const int* __restrict__ row_slot, const int* __restrict__ row_pos,
@@ -532,6 +549,13 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         const size_t head = (size_t)b * n_q + kvh * G + row;
         if (n_splits == 1) {
             out[head * D + d] = __float2bfloat16_rn(acc / l);
+        } else if (CLUSTER) {
+            float* stage_ml = reinterpret_cast<float*>(v_smem) + 16 * 32 + 16;     // [16][2], then [16][D]
+            stage_ml[32 + e] = acc;
+            if (d == 0) {
+                stage_ml[row * 2] = m;
+                stage_ml[row * 2 + 1] = l;
+            }
         } else {
             __stcg(part_o + (head * n_splits + split) * D + d, acc);
             if (d == 0) {
@@ -539,6 +563,38 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
                 __stcg(part_ml + (head * n_splits + split) * 2 + 1, l);
             }
         }
+    }
+    if (CLUSTER) {
+        // no early return above in this mode: every thread of every block reaches both barriers
+        cluster_sync_all();
+        if (split == 0 && n_splits > 1) {
+            const float* stage_ml = reinterpret_cast<const float*>(v_smem) + 16 * 32 + 16;
+            float* w_smem = reinterpret_cast<float*>(v_smem);            // [16][32]
+            float* l_total = w_smem + 16 * 32;                           // [16]
+            for (int row = warp; row < G; row += 4) {
+                const float ms = lane < n_splits ? load_from_block(stage_ml + row * 2, (uint32_t)lane) : -INFINITY;
+                const float ls = lane < n_splits ? load_from_block(stage_ml + row * 2 + 1, (uint32_t)lane) : 0.f;
+                const float m = warp_max(ms);
+                const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - m);
+                const float l = warp_sum(ls * wgt);
+                w_smem[row * 32 + lane] = wgt;
+                if (lane == 0) l_total[row] = l;
+            }
+            __syncthreads();
+            for (int e = threadIdx.x; e < G * D; e += kThreads) {
+                const int row = e / D, d = e % D;
+                const size_t head = (size_t)b * n_q + kvh * G + row;
+                float v[8];                                               // n_splits <= 8 in this mode
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = j < n_splits ? load_from_block(stage_ml + 32 + e, (uint32_t)j) : 0.f;
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc += v[j] * w_smem[row * 32 + j];
+                out[head * D + d] = __float2bfloat16_rn(acc / l_total[row]);
+            }
+        }
+        cluster_sync_all();
+        return;
     }
     if (n_splits == 1 || counters == nullptr) return;
 
@@ -626,11 +682,11 @@ int launch_prefill(void* out, const void* q, const int* tile_row0, const int* ti
     return thn_launch_status("attention_prefill");
 }
 
-template <int D, int STAGES, bool FUSED>
+template <int D, int STAGES, bool FUSED, bool CLUSTER>
 int configure_decode() {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, FUSED>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, FUSED, CLUSTER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)decode_smem<D, STAGES>());
         if (e != cudaSuccess) {
@@ -643,11 +699,14 @@ int configure_decode() {
     return THN_OK;
 }
 
+constexpr int kMaxClusterSplits = 8;      // the portable cluster size
+int g_decode_cluster = 1;
+
 template <int D>
 int decode_blocks_per_sm() {
-    if (configure_decode<D, 2, false>() != THN_OK) return 1;
+    if (configure_decode<D, 2, false, false>() != THN_OK) return 1;
     int blocks = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2, false>, kThreads,
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2, false, false>, kThreads,
                                                                   decode_smem<D, 2>());
     return (e == cudaSuccess && blocks > 0) ? blocks : 1;
 }
@@ -656,15 +715,24 @@ template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
                   cudaStream_t stream, FusedInput fused = FusedInput{}) {
-    int configured = n_splits == 1 ? configure_decode<D, 3, FUSED>() : configure_decode<D, 2, FUSED>();
-    if (configured != THN_OK) return configured;
     dim3 grid(n_seqs, kv.n_kv, n_splits);
+    if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster) {
+        // the splits of a (sequence, kv head) as one cluster along z
+        int configured = configure_decode<D, 2, FUSED, true>();
+        if (configured != THN_OK) return configured;
+        thn_launch_cluster(attention_decode_kernel<D, 2, FUSED, true>, grid, kThreads, decode_smem<D, 2>(), stream,
+                           dim3(1, 1, n_splits), (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot,
+                           row_pos, kv, n_q, n_splits, scale * kLog2e, window, counters, err, fused);
+        return thn_launch_status("attention_decode (cluster)");
+    }
+    int configured = n_splits == 1 ? configure_decode<D, 3, FUSED, false>() : configure_decode<D, 2, FUSED, false>();
+    if (configured != THN_OK) return configured;
     if (n_splits == 1)
-        thn_launch(attention_decode_kernel<D, 3, FUSED>, grid, kThreads, decode_smem<D, 3>(), stream,
+        thn_launch(attention_decode_kernel<D, 3, FUSED, false>, grid, kThreads, decode_smem<D, 3>(), stream,
                    (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
                    scale * kLog2e, window, counters, err, fused);
     else
-        thn_launch(attention_decode_kernel<D, 2, FUSED>, grid, kThreads, decode_smem<D, 2>(), stream,
+        thn_launch(attention_decode_kernel<D, 2, FUSED, false>, grid, kThreads, decode_smem<D, 2>(), stream,
                    (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
                    scale * kLog2e, window, counters, err, fused);
     int status = thn_launch_status("attention_decode");
@@ -715,6 +783,11 @@ THN_API long long thn_attention_decode_scratch_floats(int n_seqs, int n_q, int n
 THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
     return head_dim == 64 ? decode_blocks_per_sm<64>() : decode_blocks_per_sm<128>();
 }
+
+// 0: the splits of a sequence always meet in global memory; 1 (default): in a thread-block
+// cluster's shared memory when there are at most thn_attention_decode_cluster_splits() of them.
+THN_API void thn_set_decode_cluster(int enabled) { g_decode_cluster = enabled ? 1 : 0; }
+THN_API int thn_attention_decode_cluster_splits() { return g_decode_cluster ? kMaxClusterSplits : 0; }
 
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
 // counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the

@@ -83,6 +83,27 @@ inline void thn_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t 
     cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads cudaGetLastError
 }
 
+// The same with the blocks grouped into thread-block clusters of the given shape.
+template <typename... Params, typename... Args>
+inline void thn_launch_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               dim3 cluster, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster.x;
+    attribute[0].val.clusterDim.y = cluster.y;
+    attribute[0].val.clusterDim.z = cluster.z;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = g_thn_pdl ? 2 : 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // the caller reads cudaGetLastError
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
+    "thn_attention_decode_cluster_splits": [],
     "thn_attention_prefill_tile_rows": [],
     "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
@@ -89,6 +90,9 @@ def lib():
         loaded.thn_set_pdl.argtypes = [c_int]
         loaded.thn_set_pdl.restype = None
         loaded.thn_set_pdl(0 if os.environ.get("THN_PDL", "1").strip().lower() in ("0", "false", "no", "off") else 1)
+        loaded.thn_set_decode_cluster.argtypes = [c_int]
+        loaded.thn_set_decode_cluster.restype = None
+        loaded.thn_set_decode_cluster(0 if os.environ.get("THN_DECODE_CLUSTER", "1").strip() in ("0", "false", "off") else 1)
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -528,7 +532,8 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128) -> int:
     GPU with one wave of blocks.  It depends on the batch only, never on the lengths, so a captured
     step stays valid while the sequences grow."""
     capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
-    return max(1, min(16, capacity // max(1, n_seqs * n_kv)))
+    most = lib().thn_attention_decode_cluster_splits() or 16      # a cluster holds at most 8 blocks
+    return max(1, min(most, capacity // max(1, n_seqs * n_kv)))
 
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
