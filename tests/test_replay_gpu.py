@@ -71,6 +71,28 @@ def test_unequal_batches_with_slot_reuse(tiny_models, tmp_path, name, dtype):
             assert np.array_equal(got[r], alone[r]), f"{r}: float32 logits depend on the batch"
 
 
+@pytest.mark.parametrize("policy", ["auto", "all"])
+@pytest.mark.parametrize("name", NAMES)
+def test_single_token_steps_through_the_streaming_product(tiny_models, tmp_path, name, policy, monkeypatch):
+    """At the tiny sizes the few-row products would all go to the vendor library.  Here every
+    product of a step of at most 16 rows is sent to this library's weight-streaming kernel
+    (``all``: the gate-up product fused with SwiGLU as well), the head with float32 output
+    included, and the logits are held to the same measure."""
+    from thing_htn_2026_b200 import ops
+    monkeypatch.setattr(ops, "STREAM_MIN_K", 0)
+    monkeypatch.setattr(ops, "STREAM_MIN_N", 0)
+    monkeypatch.setattr(ops, "STREAM_POLICY", policy)
+    before = ops.launch_count
+    requests = make_requests(name, [40, 33, 97], seed0=30)
+    got = harness.replay(tiny_models[name], "bfloat16", harness.trace_tail(requests, 32), str(tmp_path))
+    harness.check_against_plain(got, requests, tiny_models[name], "bfloat16", f"streaming products ({policy})")
+    batches = [{k: requests[k] for k in ("r0", "r1")}, {"r2": requests["r2"]}]
+    mixed = harness.replay(tiny_models[name], "bfloat16", harness.trace_batches(batches, {"r0": 7, "r1": 33, "r2": 64}),
+                           str(tmp_path / "b"))
+    harness.check_against_plain(mixed, requests, tiny_models[name], "bfloat16", f"streaming products, batches ({policy})")
+    assert ops.launch_count > before
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["a", "c", "d"])
 def test_long_decoding(tiny_models, tmp_path, name, dtype):
