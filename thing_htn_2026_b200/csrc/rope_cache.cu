@@ -88,10 +88,9 @@ __global__ void qk_norm_rope_cache_kernel(
 // The serving case: bfloat16 tensor input, head sizes 64, 128 and 256, full rotation.  A lane
 // owns E = D / 64 consecutive values in each half of the head, so the partner of every value
 // it rotates is its own: no shared memory, 4-byte or wider accesses, same arithmetic.  A warp
-// takes H consecutive heads of one row: their loads are all in flight before the first is
-// used, and the row's position, page and angles are fetched once.  Steps of few rows take
-// H = 1, so that every head has a warp of its own.
-constexpr int kHeadsPerWarp = 4;
+// takes H consecutive heads of one row (their loads all in flight before the first is used);
+// single-token steps use H = 1, so that every head has a warp of its own, and steps of more
+// than kFewRows rows use the 16-byte kernel further down.
 constexpr int kFewRows = 64;
 
 template <typename WT, int D, int H>
@@ -184,6 +183,145 @@ __global__ void qk_norm_rope_cache_bf16_kernel(
     }
 }
 
+// Steps of many rows (prompts): the same arithmetic with 16-byte accesses.  A head is spread
+// over L = D / 8 lanes, eight consecutive values each, so a warp takes 32 / L heads per pass
+// and kVecPasses passes whose loads are all in flight together; the value a lane rotates with
+// lives L / 2 lanes away and comes by shuffle; the sum of squares is reduced over the L
+// lanes of the head.
+constexpr int kVecPasses = 4;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+template <typename WT>
+__device__ __forceinline__ void load_gain8(const WT* gain, int d, float (&g)[8]);
+template <>
+__device__ __forceinline__ void load_gain8<__nv_bfloat16>(const __nv_bfloat16* gain, int d, float (&g)[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(gain + d), g);
+}
+template <>
+__device__ __forceinline__ void load_gain8<float>(const float* gain, int d, float (&g)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(gain + d), b = *reinterpret_cast<const float4*>(gain + d + 4);
+    g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+}
+
+template <typename WT, int D>
+__global__ void qk_norm_rope_cache_bf16_vec_kernel(
+    __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ q_gain,
+    const WT* __restrict__ k_gain, float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+    int table_len, const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_rows, int n_q,
+    int write_cache, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
+    using B = __nv_bfloat16;
+    constexpr int L = D / 8, kHalf = D / 2, kPerPass = 32 / L, kPerWarp = kPerPass * kVecPasses;
+    const int lane = threadIdx.x & 31;
+    const int n_heads_total = n_q + 2 * kv.n_kv;
+    const int n_used = write_cache ? n_heads_total : n_q;
+    const int groups = (n_used + kPerWarp - 1) / kPerWarp;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (long long)n_rows * groups) return;
+    const int m = (int)(unit / groups), head0 = (int)(unit - (long long)m * groups) * kPerWarp;
+    const int sub = lane / L, l = lane % L;            // which head of the pass, which eighth of it
+    const int d = 8 * l;                               // this lane's values: [d, d + 8)
+    const __nv_bfloat16* row = qkv + (size_t)m * n_heads_total * D;
+
+    uint4 raw[kVecPasses];
+#pragma unroll
+    for (int p = 0; p < kVecPasses; ++p) {
+        const int head = head0 + p * kPerPass + sub;
+        raw[p] = head < n_used ? *reinterpret_cast<const uint4*>(row + (size_t)head * D + d) : make_uint4(0, 0, 0, 0);
+    }
+    const int pos = row_pos[m];
+    if (pos >= table_len) {
+        if (lane == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+        return;
+    }
+    // angles of this lane's values: index d mod D/2 in the row's table
+    float c[8], sn[8];
+    {
+        const float* cr = cos_tab + (size_t)pos * kHalf + (d % kHalf);
+        const float* sr = sin_tab + (size_t)pos * kHalf + (d % kHalf);
+        const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+        const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c[i] = rnd<B>(cc[i]);
+            sn[i] = rnd<B>(ss[i]);
+        }
+    }
+    int page = 0;
+    if (head0 + kPerWarp > n_q && write_cache) {
+        page = kv.block_table[(size_t)row_slot[m] * kv.bt_stride + pos / kv.page_size];
+        if (page < 0) {
+            if (lane == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+            return;
+        }
+    }
+    const bool upper = d >= kHalf;                     // this lane holds the second half of the head
+#pragma unroll
+    for (int p = 0; p < kVecPasses; ++p) {
+        const int head = head0 + p * kPerPass + sub;   // may differ between the lanes of a warp
+        const bool live = head < n_used;
+        const bool is_q = head < n_q, is_k = !is_q && head < n_q + kv.n_kv;
+        float x[8];
+        unpack8(raw[p], x);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+        for (int off = 1; off < L; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        float g[8];
+        load_gain8<WT>(is_q ? q_gain : k_gain, d, g);
+        uint4 mine;                                    // gain * normalised value, rounded, as bfloat16 pairs
+        {
+            __nv_bfloat162* mp = reinterpret_cast<__nv_bfloat162*>(&mine);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                mp[i] = __floats2bfloat162_rn(g[2 * i] * rnd<B>(x[2 * i] * rstd), g[2 * i + 1] * rnd<B>(x[2 * i + 1] * rstd));
+        }
+        uint4 other;                                   // the same of the lane L / 2 away
+        other.x = __shfl_xor_sync(0xffffffffu, mine.x, L / 2);
+        other.y = __shfl_xor_sync(0xffffffffu, mine.y, L / 2);
+        other.z = __shfl_xor_sync(0xffffffffu, mine.z, L / 2);
+        other.w = __shfl_xor_sync(0xffffffffu, mine.w, L / 2);
+        if (!live) continue;
+        __nv_bfloat16* dst;
+        if (is_q) {
+            dst = q_out + (size_t)m * n_q * D + (size_t)head * D + d;
+        } else {
+            const int kvh = is_k ? head - n_q : head - n_q - kv.n_kv;
+            dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, is_k ? 0 : 1, kvh, pos % kv.page_size) + d;
+        }
+        if (!is_q && !is_k) {                          // V: plain copy
+            *reinterpret_cast<uint4*>(dst) = raw[p];
+            continue;
+        }
+        float a[8], b[8];
+        unpack8(mine, a);
+        unpack8(other, b);
+        uint4 res;
+        __nv_bfloat16* rp = reinterpret_cast<__nv_bfloat16*>(&res);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            // first half: x0 * c - x1 * s with x1 from the partner; second half: x1 * c + x0 * s
+            const float rotated = upper ? rnd<B>(b[i] * sn[i]) : rnd<B>(-b[i] * sn[i]);
+            rp[i] = __float2bfloat16_rn(rnd<B>(a[i] * c[i]) + rotated);
+        }
+        *reinterpret_cast<uint4*>(dst) = res;
+    }
+}
+
 // qkv [n_rows, (n_q + 2*n_kv) * head_dim] -> q_out [n_rows, n_q * head_dim]; K and V of
 // every row go to (slot, position) of the cache entry unless write_cache == 0.
 // q_gain/k_gain may be null (no head norm); cos_tab may be null (no rotation).
@@ -210,17 +348,21 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
     const long long part_stride = (long long)n_rows * (n_q + 2 * n_kv) * head_dim;
     if (dtype == THN_BF16 && qkv && q_gain && cos_tab && rotary_dim == head_dim &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
-        const int per_warp = n_rows <= kFewRows ? 1 : kHeadsPerWarp;
-        const long long fast_units = (long long)n_rows * ((n_q + 2 * n_kv + per_warp - 1) / per_warp);
+        const bool many = n_rows > kFewRows && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kv_base |
+                                                  (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos_tab |
+                                                  (uintptr_t)sin_tab) & 15) == 0;
+        const int per_pass = 32 / (head_dim / 8);
+        const int n_used = write_cache ? n_q + 2 * n_kv : n_q;
+        const long long fast_units = many ? (long long)n_rows * ((n_used + per_pass * kVecPasses - 1) / (per_pass * kVecPasses))
+                                          : (long long)n_rows * (n_q + 2 * n_kv);
         const unsigned fast_blocks = (unsigned)((fast_units + warps - 1) / warps);
-#define FAST_H(WT, D, H)                                                                                            \
-    thn_launch(qk_norm_rope_cache_bf16_kernel<WT, D, H>, fast_blocks, warps * 32, 0, stream, \
-        (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, (const WT*)q_gain, (const WT*)k_gain, eps, cos_tab,       \
-        sin_tab, table_len, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)
+#define FAST_ARGS(WT)                                                                                               \
+    (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, (const WT*)q_gain, (const WT*)k_gain, eps, cos_tab, sin_tab,  \
+        table_len, row_slot, row_pos, kv, n_rows, n_q, write_cache, err
 #define FAST(WT, D)                                                                                                 \
     do {                                                                                                            \
-        if (per_warp == 1) FAST_H(WT, D, 1);                                                                        \
-        else FAST_H(WT, D, kHeadsPerWarp);                                                                          \
+        if (many) thn_launch(qk_norm_rope_cache_bf16_vec_kernel<WT, D>, fast_blocks, warps * 32, 0, stream, FAST_ARGS(WT)); \
+        else thn_launch(qk_norm_rope_cache_bf16_kernel<WT, D, 1>, fast_blocks, warps * 32, 0, stream, FAST_ARGS(WT)); \
     } while (0)
         bool done = true;
         if (w_dtype == THN_BF16 && head_dim == 64) FAST(__nv_bfloat16, 64);
@@ -231,7 +373,7 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
         else if (w_dtype == THN_F32 && head_dim == 256) FAST(float, 256);
         else done = false;
 #undef FAST
-#undef FAST_H
+#undef FAST_ARGS
         if (done) return thn_launch_status("qk_norm_rope_cache");
     }
 #define LAUNCH(T, WT)                                                                                              \
