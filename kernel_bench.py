@@ -67,6 +67,34 @@ def prefill_products(args):
             entry.update({"own_fused_swiglu_us": fused, "library_plus_swiglu_us": both})
         print(f"gemm_{name}_m{m}", json.dumps({k_: round(v, 2) for k_, v in entry.items()}))
         del weights
+    # the kernels between the products, at their prompt sizes (inputs rotate through more than L2 holds)
+    from thing_htn_2026_b200.cache import KVSpec, SequenceCache
+    from thing_htn_2026_b200.config.base import PartSpec
+    from thing_htn_2026_b200.parts import Runtime, part_class
+    copies = 4
+    gus = [torch.randn(m, 2 * I, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    us = time_cold(lambda i: ops.swiglu(gus[i]), copies, args.reps)
+    print(f"swiglu_m{m}", json.dumps({"own_us": round(us, 2), "gbs": round(m * 3 * I * 2 / us / 1e3, 1)}))
+    del gus
+    hs = [torch.randn(m, H, device=dev, dtype=torch.bfloat16) for _ in range(16)]
+    ds = [torch.randn(m, H, device=dev, dtype=torch.bfloat16) for _ in range(16)]
+    gain = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    us = time_cold(lambda i: ops.add_rmsnorm(hs[i], ds[i], gain, 1e-6), 16, args.reps)
+    print(f"add_rmsnorm_m{m}", json.dumps({"own_us": round(us, 2), "gbs": round(m * 4 * H * 2 / us / 1e3, 1)}))
+    del hs, ds
+    cache = SequenceCache([KVSpec(NKV, D)] * copies, max_tokens=m + 64, dtype=torch.bfloat16, device=dev, max_slots=2)
+    (slot,) = cache.open(1)
+    cache.prepare([slot], [m])
+    cu = torch.tensor([0, m], dtype=torch.int32, device=dev)
+    rows = ops.step_rows(cu, torch.tensor([slot], dtype=torch.int32, device=dev), cache.seq_lens, m, m)
+    rope = part_class("position", "rope")(PartSpec("rope", {"head_dim": D, "theta": 1e6}), Runtime(torch.bfloat16, torch.device(dev), {}))
+    rope.ensure(m + 64)
+    qkvs = [torch.randn(m, (NQ + 2 * NKV) * D, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    views = [cache.kv_view(e) for e in range(copies)]
+    us = time_cold(lambda i: ops.qk_norm_rope_cache(qkvs[i], gain[:D], gain[:D], 1e-6, rope.tables(), rows, views[i], NQ,
+                                                     True, err), copies, args.reps)
+    nbytes = m * ((NQ + 2 * NKV) * D * 2 + (NQ + 2 * NKV) * D * 2)
+    print(f"qk_norm_rope_cache_m{m}", json.dumps({"own_us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)}))
     assert int(err.item()) == 0
 
 

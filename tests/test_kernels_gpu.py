@@ -404,6 +404,40 @@ def test_attention_window_edge(kernel, dtype):
     close(got, want, dtype, "window edge", scale=4)
 
 
+@pytest.mark.parametrize("gain_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n_q,n_kv,D", [(5, 1, 64), (8, 2, 128), (3, 1, 256)])
+def test_qk_norm_rope_cache_same_bits_for_long_and_short_steps(n_q, n_kv, D, gain_dtype):
+    """Steps of many rows go through another kernel (16-byte accesses, paired bfloat16
+    products) than steps of few rows; a token's q and its cache entry must not depend on
+    which one it met: 200 rows in one step against the same rows in steps of 50."""
+    from thing_htn_2026_b200.config.base import PartSpec
+    from thing_htn_2026_b200.parts import Runtime, part_class
+    o = ops()
+    dtype = torch.bfloat16
+    rope = part_class("position", "rope")(PartSpec("rope", {"head_dim": D, "theta": 4321.0}),
+                                          Runtime(dtype, torch.device(DEV), {}))
+    rope.ensure(256)
+    qkv = rand((200, (n_q + 2 * n_kv) * D), dtype, 80, 2.0).to(DEV)
+    qg = (1 + 0.3 * torch.randn(D, generator=torch.Generator().manual_seed(81))).to(gain_dtype).to(DEV)
+    kg = (1 + 0.3 * torch.randn(D, generator=torch.Generator().manual_seed(82))).to(gain_dtype).to(DEV)
+    err = o.new_error_word(DEV)
+    results = []
+    for chunk in (200, 50):
+        fix = PagedFixture(n_kv, D, [200], dtype)
+        parts = []
+        for start in range(0, 200, chunk):
+            rows, _ = fix.rows([chunk])
+            parts.append(o.qk_norm_rope_cache(qkv[start:start + chunk].contiguous(), qg, kg, 1e-6, rope.tables(), rows,
+                                              fix.kv, n_q, True, err))
+            fix.advance(rows, [chunk])
+        results.append((torch.cat(parts), fix.kv.storage.clone(), fix.kv.block_table.clone()))
+    assert int(err.item()) == 0
+    (q_long, cache_long, table_long), (q_short, cache_short, table_short) = results
+    assert torch.equal(table_long, table_short)
+    assert torch.equal(q_long, q_short), "q depends on the length of the step"
+    assert torch.equal(cache_long, cache_short), "the cache depends on the length of the step"
+
+
 # ----------------------------------------------------------------------------- fused single-token step
 
 

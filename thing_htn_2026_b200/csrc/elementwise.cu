@@ -259,13 +259,18 @@ __global__ void swiglu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __
         const uint4 uv = *reinterpret_cast<const uint4*>(gu + (m * 2 * inter_vecs + inter_vecs + i) * 8);
         const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(&gv);
         const __nv_bfloat16* ub = reinterpret_cast<const __nv_bfloat16*>(&uv);
+        // silu in float32 with the fast exponential and reciprocal (a few float32 ulp, far below
+        // the bfloat16 rounding that follows); the product of the two bfloat16 values with the
+        // paired instruction, which rounds the exact product once as the reference's does.
         uint4 ov;
-        __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&ov);
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&ov);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(gb);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(ub);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float g = __bfloat162float(gb[j]);
-            const float s = rnd<__nv_bfloat16>(g / (1.0f + expf(-g)));
-            ob[j] = __float2bfloat16_rn(s * __bfloat162float(ub[j]));
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]);
+            const float s0 = __fdividef(g.x, 1.0f + __expf(-g.x)), s1 = __fdividef(g.y, 1.0f + __expf(-g.y));
+            ob[j] = __hmul2(__floats2bfloat162_rn(s0, s1), u2[j]);
         }
         *reinterpret_cast<uint4*>(out + e * 8) = ov;
     }

@@ -245,7 +245,10 @@ __global__ void qk_norm_rope_cache_bf16_vec_kernel(
         return;
     }
     // angles of this lane's values: index d mod D/2 in the row's table
-    float c[8], sn[8];
+    // (a bfloat16 product of two bfloat16 values is their exact product rounded once, which
+    // is what rounding the float32 product gives: the paired instructions do four roundings of
+    // the reference's formula at a quarter of the instructions)
+    __nv_bfloat162 c2[4], s2[4];
     {
         const float* cr = cos_tab + (size_t)pos * kHalf + (d % kHalf);
         const float* sr = sin_tab + (size_t)pos * kHalf + (d % kHalf);
@@ -254,9 +257,9 @@ __global__ void qk_norm_rope_cache_bf16_vec_kernel(
         const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c[i] = rnd<B>(cc[i]);
-            sn[i] = rnd<B>(ss[i]);
+        for (int i = 0; i < 4; ++i) {
+            c2[i] = __floats2bfloat162_rn(cc[2 * i], cc[2 * i + 1]);
+            s2[i] = __floats2bfloat162_rn(ss[2 * i], ss[2 * i + 1]);
         }
     }
     int page = 0;
@@ -287,8 +290,15 @@ __global__ void qk_norm_rope_cache_bf16_vec_kernel(
         {
             __nv_bfloat162* mp = reinterpret_cast<__nv_bfloat162*>(&mine);
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                mp[i] = __floats2bfloat162_rn(g[2 * i] * rnd<B>(x[2 * i] * rstd), g[2 * i + 1] * rnd<B>(x[2 * i + 1] * rstd));
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 normed = __floats2bfloat162_rn(x[2 * i] * rstd, x[2 * i + 1] * rstd);
+                if (sizeof(WT) == 2) {
+                    mp[i] = __hmul2(__floats2bfloat162_rn(g[2 * i], g[2 * i + 1]), normed);
+                } else {                               // float32 gains: the product is rounded from float32
+                    const float2 nf = __bfloat1622float2(normed);
+                    mp[i] = __floats2bfloat162_rn(g[2 * i] * nf.x, g[2 * i + 1] * nf.y);
+                }
+            }
         }
         uint4 other;                                   // the same of the lane L / 2 away
         other.x = __shfl_xor_sync(0xffffffffu, mine.x, L / 2);
@@ -307,16 +317,16 @@ __global__ void qk_norm_rope_cache_bf16_vec_kernel(
             *reinterpret_cast<uint4*>(dst) = raw[p];
             continue;
         }
-        float a[8], b[8];
-        unpack8(mine, a);
-        unpack8(other, b);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&mine);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&other);
         uint4 res;
-        __nv_bfloat16* rp = reinterpret_cast<__nv_bfloat16*>(&res);
+        __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&res);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             // first half: x0 * c - x1 * s with x1 from the partner; second half: x1 * c + x0 * s
-            const float rotated = upper ? rnd<B>(b[i] * sn[i]) : rnd<B>(-b[i] * sn[i]);
-            rp[i] = __float2bfloat16_rn(rnd<B>(a[i] * c[i]) + rotated);
+            const float2 p1 = __bfloat1622float2(__hmul2(ap[i], c2[i]));
+            const float2 p2 = __bfloat1622float2(__hmul2(upper ? bp[i] : __hneg2(bp[i]), s2[i]));
+            rp[i] = __floats2bfloat162_rn(p1.x + p2.x, p1.y + p2.y);       // the sum in float32, rounded once
         }
         *reinterpret_cast<uint4*>(dst) = res;
     }
