@@ -12,12 +12,15 @@
 //                  128-byte swizzle, K-major), S in 64 columns of tensor memory;
 //   softmax        each thread reads its row of S (tcgen05.ld), masks, takes the running
 //                  maximum, rescales the output accumulator in tensor memory when the
-//                  maximum moved, writes exp2 of its row as bfloat16 to shared memory (P);
-//   O += P V       tcgen05.mma, M 128, N 128, K 16 x 4; P K-major from shared memory, the V
-//                  page as it lies in the cache ([key][d]: the N index contiguous, an
+//                  maximum moved, and writes exp2 of its row as bfloat16 pairs back into the
+//                  first 32 columns of the S buffer it came from (tcgen05.st): that is P;
+//   O += P V       tcgen05.mma, M 128, N 128, K 16 x 4; P as the operand from tensor memory,
+//                  the V page as it lies in the cache ([key][d]: the N index contiguous, an
 //                  MN-major operand), O in 128 columns of tensor memory.
 // K and V pages come through a two-stage ring filled by TMA from a tensor map over the
-// cache entry.  The steps of one tile run one after another; two blocks per SM overlap.
+// cache entry.  S has two buffers, so S of tile t + 1 is multiplied while the softmax warps
+// work on tile t, and since P lives in its own S buffer nothing but the tensor core's own
+// order stands between one tile's O += P V and the next tile's softmax.  Two blocks per SM.
 //
 // Every wait on an mbarrier is bounded (see gemm_tcgen05.cu); a waiter that gives up sets
 // THN_ERR_WAIT_TIMEOUT and all roles leave through the common exit.
@@ -36,9 +39,8 @@ constexpr int kColS = 0, kColO = 128;
 constexpr uint32_t kQBytes = kRows * D * 2;       // 32 KB: two [128 x 64] swizzled blocks
 constexpr uint32_t kKBytes = kKeys * D * 2;       // 16 KB: two [64 x 64] blocks
 constexpr uint32_t kVBytes = kKeys * D * 2;       // 16 KB: two [64 keys x 64 d] blocks
-constexpr uint32_t kPBytes = kRows * kKeys * 2;   // 16 KB: one [128 x 64] block
 constexpr uint32_t kStageBytes = kKBytes + kVBytes;
-constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 128;   // two blocks fit one SM
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + 128;   // two blocks fit one SM
 constexpr unsigned long long kWaitLimitNs = 20ull * 1000 * 1000;   // a wait gives up after 20 ms
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -119,6 +121,19 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
         ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with the 128-row operand read from tensor memory: lane = row, a 32-bit column holds
+// two consecutive k.
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -170,12 +185,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     extern __shared__ __align__(1024) unsigned char smem_raw[];      // swizzled tiles want 1024-byte alignment
     unsigned char* q_smem = smem_raw;
     unsigned char* kv_smem = q_smem + kQBytes;                         // [stage][K 16 KB | V 16 KB]
-    unsigned char* p_smem = kv_smem + kStages * kStageBytes;
-    uint64_t* q_full = reinterpret_cast<uint64_t*>(p_smem + kPBytes);
-    uint64_t* kv_full = q_full + 1;              // [kStages]
-    uint64_t* kv_empty = kv_full + kStages;      // [kStages]
-    uint64_t* s_full = kv_empty + kStages;       // [2] S = Q K^T of a tile is in tensor memory (two buffers)
-    uint64_t* p_ready = s_full + 2;              // P of this tile is in shared memory (4 arrivals)
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(kv_smem + kStages * kStageBytes);
+    uint64_t* k_full = q_full + 1;               // [kStages] the K page of a tile is in shared memory
+    uint64_t* k_empty = k_full + kStages;        // [kStages] ... and has been multiplied (free after S = Q K^T)
+    uint64_t* v_full = k_empty + kStages;        // [kStages] the same for the V page
+    uint64_t* v_empty = v_full + kStages;        // [kStages] (free after O += P V)
+    uint64_t* s_full = v_empty + kStages;        // [2] S = Q K^T of a tile is in tensor memory (two buffers)
+    uint64_t* p_ready = s_full + 2;              // P of this tile is in tensor memory (4 arrivals)
     uint64_t* o_full = p_ready + 1;              // O += P V of this tile is done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -193,8 +209,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(kv_full + s, 1);
-            mbar_init(kv_empty + s, 1);
+            mbar_init(k_full + s, 1);
+            mbar_init(k_empty + s, 1);
+            mbar_init(v_full + s, 1);
+            mbar_init(v_empty + s, 1);
         }
         mbar_init(s_full, 1);
         mbar_init(s_full + 1, 1);
@@ -218,29 +236,36 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         mbar_expect_tx(q_full, kQBytes);
         tma_load_2d(q_smem, &map_q, q_full, h * D, row0);
         tma_load_2d(q_smem + kQBytes / 2, &map_q, q_full, h * D + 64, row0);
-        int it = 0;
-        for (int t = t_first; t <= t_last && !*give_up; ++t, ++it) {
+        // K pages and V pages have rings of their own: a K page is free again once S = Q K^T has
+        // read it, long before the tile's V page, so K runs one tile further ahead: K(0), K(1),
+        // V(0), K(2), V(1), ...
+        const int n_it = t_last - t_first + 1;
+        auto load = [&](int it, int which) {        // which: 0 = K, 1 = V
             const int s = it % kStages;
-            if (!mbar_wait(kv_empty + s, ((it / kStages) & 1) ^ 1)) {
+            uint64_t* empty = which ? v_empty : k_empty;
+            uint64_t* full = which ? v_full : k_full;
+            if (!mbar_wait(empty + s, ((it / kStages) & 1) ^ 1)) {
                 if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
-                *give_up = 1;
-                break;
+                return false;
             }
-            const int page = pages[t];
+            const int page = pages[t_first + it];
             if (page < 0) {
                 if (err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
-                *give_up = 1;
-                break;
+                return false;
             }
-            unsigned char* k_dst = kv_smem + (size_t)s * kStageBytes;
-            unsigned char* v_dst = k_dst + kKBytes;
-            const int k_row = ((page * 2 + 0) * n_kv + kvh) * kKeys, v_row = ((page * 2 + 1) * n_kv + kvh) * kKeys;
-            mbar_expect_tx(kv_full + s, kStageBytes);
-            tma_load_2d(k_dst, &map_kv, kv_full + s, 0, k_row);
-            tma_load_2d(k_dst + kKBytes / 2, &map_kv, kv_full + s, 64, k_row);
-            tma_load_2d(v_dst, &map_kv, kv_full + s, 0, v_row);
-            tma_load_2d(v_dst + kVBytes / 2, &map_kv, kv_full + s, 64, v_row);
+            unsigned char* dst = kv_smem + (size_t)s * kStageBytes + (which ? kKBytes : 0);
+            const int row = ((page * 2 + which) * n_kv + kvh) * kKeys;
+            mbar_expect_tx(full + s, kKBytes);
+            tma_load_2d(dst, &map_kv, full + s, 0, row);
+            tma_load_2d(dst + kKBytes / 2, &map_kv, full + s, 64, row);
+            return true;
+        };
+        bool ok = n_it <= 0 || load(0, 0);
+        for (int it = 0; it < n_it && ok && !*give_up; ++it) {
+            if (it + 1 < n_it) ok = load(it + 1, 0);
+            if (ok) ok = load(it, 1);
         }
+        if (!ok) *give_up = 1;
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer.  S of tile it + 1 is multiplied while the softmax warps work on
         // tile it; O += P V of tile it follows as soon as its P is ready.
@@ -249,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         const uint32_t q_addr = smem_addr(q_smem);
         auto qk = [&](int it) {          // S[it & 1] = Q K(it)^T
             const int s = it % kStages;
-            if (!mbar_wait(kv_full + s, (it / kStages) & 1)) return false;
+            if (!mbar_wait(k_full + s, (it / kStages) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t k_addr = smem_addr(kv_smem + (size_t)s * kStageBytes);
             // eight k steps of 16 d; d 0-63 in the first swizzled block, 64-127 in the second
@@ -259,6 +284,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 const uint64_t b = desc_k_major(k_addr + (k / 4) * (kKBytes / 2) + (k % 4) * 32);
                 umma(tmem_base + kColS + (it & 1) * kKeys, a, b, kDescS, k != 0);
             }
+            umma_commit(k_empty + s);             // the K page is free when these products are done
             umma_commit(s_full + (it & 1));
             return true;
         };
@@ -268,19 +294,21 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 ok = qk(it + 1);
                 if (!ok) break;
             }
-            ok = mbar_wait(p_ready, it & 1);      // P is in shared memory; O has been rescaled
+            ok = mbar_wait(p_ready, it & 1);      // P is in tensor memory; O has been rescaled
+            if (!ok) break;
+            const int s = it % kStages;
+            ok = mbar_wait(v_full + s, (it / kStages) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int s = it % kStages;
             const uint32_t v_addr = smem_addr(kv_smem + (size_t)s * kStageBytes) + kKBytes;
-            // O += P V: four k steps of 16 keys; V rows are keys, 16 keys = 2048 bytes further
+            // O += P V: four k steps of 16 keys; P: 8 columns of bfloat16 pairs per step, in the
+            // S buffer of this tile; V rows are keys, 16 keys = 2048 bytes further
 #pragma unroll
             for (int k = 0; k < kKeys / 16; ++k) {
-                const uint64_t a = desc_k_major(smem_addr(p_smem) + k * 32);
                 const uint64_t b = desc_mn_major(v_addr + k * 2048, kVBytes / 2);
-                umma(tmem_base + kColO, a, b, kDescO, (it | k) != 0);
+                umma_a_tmem(tmem_base + kColO, tmem_base + kColS + (it & 1) * kKeys + k * 8, b, kDescO, (it | k) != 0);
             }
-            umma_commit(kv_empty + s);            // the stage is free when these products are done
+            umma_commit(v_empty + s);             // the V page is free when these products are done
             umma_commit(o_full);
         }
         if (!ok) {
@@ -350,30 +378,36 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                     pb[e / 2] = __floats2bfloat162_rn(p0, p1);
                 }
             }
-            if (it > 0) {
-                // the previous O += P V must be complete before P is overwritten and O rescaled
+            // O is rescaled only when some row of the warp moved its reference point; then the
+            // previous O += P V must be complete first.  tcgen05.ld/st are warp-wide, so the whole
+            // warp goes if any of its rows must.
+            if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 ok = mbar_wait(o_full, (it - 1) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // tcgen05.ld/st are warp-wide: the whole warp rescales if any of its rows must
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 32) {
-                        float o[32];
-                        tmem_load_32(lane_base + kColO + c, o);
+                for (int c = 0; c < D; c += 32) {
+                    float o[32];
+                    tmem_load_32(lane_base + kColO + c, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= corr;
-                        tmem_store_32(lane_base + kColO + c, o);
-                    }
+                    for (int i = 0; i < 32; ++i) o[i] *= corr;
+                    tmem_store_32(lane_base + kColO + c, o);
                 }
             }
-            // into the K-major swizzled tile: row r, 16-byte chunk c at chunk (c ^ (r % 8)) of
-            // the row's 128 bytes.
-            unsigned char* p_row = p_smem + (size_t)r * 128;
+            // P over the first 32 columns of this tile's S (the row's S is in registers by now):
+            // column j holds keys 2j and 2j + 1.
+            {
+                float words[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = packed[c];
+                for (int c = 0; c < 8; ++c) {
+                    words[4 * c] = __uint_as_float(packed[c].x);
+                    words[4 * c + 1] = __uint_as_float(packed[c].y);
+                    words[4 * c + 2] = __uint_as_float(packed[c].z);
+                    words[4 * c + 3] = __uint_as_float(packed[c].w);
+                }
+                tmem_store_32(lane_base + kColS + (it & 1) * kKeys, words);
+            }
             run_sum = run_sum * corr + sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
