@@ -187,22 +187,6 @@ def test_gemm_tcgen05_fused_swiglu(m, inter, k):
     assert err_abs.pow(2).mean().sqrt() <= noise.pow(2).mean().sqrt()
 
 
-def test_consumers_take_split_sums():
-    """Kernels that read a product as partial sums give what they give on the summed tensor."""
-    o = ops()
-    m, n = 5, 200
-    parts = rand((3, m, n), torch.float32, 44).to(DEV)
-    product = o.SplitSum(parts, torch.bfloat16)
-    tensor = o.resolve(product)
-    assert torch.equal(tensor, (parts[0] + parts[1] + parts[2]).to(torch.bfloat16))
-    assert torch.equal(o.swiglu(product), o.swiglu(tensor))
-    h = rand((m, n), torch.bfloat16, 42).to(DEV)
-    h2 = h.clone()
-    gain = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(43))).to(torch.bfloat16).to(DEV)
-    assert torch.equal(o.add_rmsnorm(h, product, gain, 1e-6), o.add_rmsnorm(h2, tensor, gain, 1e-6))
-    assert torch.equal(h, h2)
-
-
 # ----------------------------------------------------------------------------- cache helpers
 
 

@@ -96,7 +96,7 @@ def test_feed_forward_part(dtype):
     weights = {"model.layers.0.mlp.gate_proj.weight": tensors["g"], "model.layers.0.mlp.up_proj.weight": tensors["u"],
                "model.layers.0.mlp.down_proj.weight": tensors["d"]}
     from thing_htn_2026_b200 import ops
-    got = ops.resolve(part.forward(x.to(DEV), None))
+    got = part.forward(x.to(DEV), None)
     close(got, plain.mlp_block(x, weights, 0, dtype), dtype, "feed-forward")
 
 
@@ -173,9 +173,9 @@ def test_attention_part_and_block(dtype, n_q, n_kv, D, window):
             x = torch.cat([xs[i][done[i]:done[i] + c] for i, c in enumerate(counts)]).to(DEV)
             if use_block:
                 h, d = block.forward(x.clone(), None, ctx, entry)
-                out = plain.add_residual(h.cpu(), ops.resolve(d).cpu(), dtype)
+                out = plain.add_residual(h.cpu(), d.cpu(), dtype)
             else:
-                out = ops.resolve(mixer.forward(x, ctx, entry)).cpu()
+                out = mixer.forward(x, ctx, entry).cpu()
             for i, c in enumerate(counts):
                 got[i].append(out[cu[i]:cu[i] + c])
                 done[i] += c

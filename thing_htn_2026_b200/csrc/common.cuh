@@ -114,43 +114,6 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32<T>(from_f32<T>(v)); }
 
-// Where a kernel reads the output of a matrix product from: a tensor of the activation
-// type, or split-K partial sums in float32 ([n_parts] slabs of part_stride elements), which
-// are added in ascending order and rounded to the activation type, as the product itself
-// would have been.
-template <typename T>
-struct Source {
-    const T* direct;
-    const float* parts;
-    int n_parts;
-    long long part_stride;
-    __device__ __forceinline__ float load(long long i) const {
-        if (parts == nullptr) return to_f32<T>(direct[i]);
-        // All loads of a batch are issued before the first add; the adds keep slab order.
-        const float* at = parts + i;
-        float s = 0.f;
-        int p = 0;
-        for (; p + 8 <= n_parts; p += 8, at += 8 * part_stride) {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = at[(long long)j * part_stride];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += v[j];
-        }
-        if (p + 4 <= n_parts) {
-            float v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = at[(long long)j * part_stride];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s += v[j];
-            p += 4;
-            at += 4 * part_stride;
-        }
-        for (; p < n_parts; ++p, at += part_stride) s += *at;
-        return rnd<T>(s);
-    }
-};
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -5,11 +5,6 @@
 // normalised value is rounded before the gain), :61-68 (residual add rounded once),
 // :74-88 (silu rounded, product rounded).  Reductions are float32 with an order fixed
 // by the block size, so a row's result does not depend on the batch it is in.
-//
-// Inputs that come from a matrix product may arrive as split-K partial sums (float32
-// [parts, rows, width]): the kernel adds the parts in ascending order and rounds the sum to
-// the activation type, which is the value the product would have stored.  The products of
-// this library add their own partials, so nothing on the product path uses this today.
 #include <cstdarg>
 #include <cstdio>
 
@@ -74,7 +69,7 @@ constexpr int kNormKeep = 16;   // values a thread keeps in registers between th
 // v = rnd(h + d), stored back to h first.  One block per row.
 template <typename T, typename WT, bool ADD>
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ y, T* __restrict__ h,
-                                                               Source<T> d, const WT* __restrict__ w, int width,
+                                                               const T* __restrict__ d, const WT* __restrict__ w, int width,
                                                                float eps) {
     pdl_launch_dependents();
     pdl_wait();
@@ -89,7 +84,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ y
         if (i < width) {
             v = to_f32<T>(h[base + i]);
             if (ADD) {
-                v = rnd<T>(v + d.load(base + i));
+                v = rnd<T>(v + to_f32<T>(d[base + i]));
                 h[base + i] = from_f32<T>(v);
             }
         }
@@ -99,7 +94,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(T* __restrict__ y
     for (int i = threadIdx.x + kNormKeep * kNormThreads; i < width; i += kNormThreads) {
         float v = to_f32<T>(h[base + i]);
         if (ADD) {
-            v = rnd<T>(v + d.load(base + i));
+            v = rnd<T>(v + to_f32<T>(d[base + i]));
             h[base + i] = from_f32<T>(v);
         }
         ss += v * v;
@@ -177,9 +172,9 @@ __global__ void __launch_bounds__(1024) rmsnorm_bf16_vec_kernel(__nv_bfloat16* _
 }
 
 template <typename WT>
-static bool launch_rmsnorm_vec(void* y, void* h, const void* d, const float* d_parts, const void* w, int rows,
+static bool launch_rmsnorm_vec(void* y, void* h, const void* d, const void* w, int rows,
                                int width, float eps, cudaStream_t stream) {
-    if (d_parts || width % 8 || width > 8192 || (((uintptr_t)y | (uintptr_t)h | (uintptr_t)d | (uintptr_t)w) & 15))
+    if (width % 8 || width > 8192 || (((uintptr_t)y | (uintptr_t)h | (uintptr_t)d | (uintptr_t)w) & 15))
         return false;
     const int threads = ((width / 8 + 31) / 32) * 32;
     if (d)
@@ -190,39 +185,29 @@ static bool launch_rmsnorm_vec(void* y, void* h, const void* d, const float* d_p
 }
 
 template <typename T, typename WT>
-static void launch_rmsnorm(void* y, void* h, Source<T> d, bool add, const void* w, int rows, int width, float eps,
+static void launch_rmsnorm(void* y, void* h, const T* d, const void* w, int rows, int width, float eps,
                            cudaStream_t stream) {
-    if (add)
+    if (d)
         thn_launch(rmsnorm_kernel<T, WT, true>, rows, kNormThreads, 0, stream, (T*)y, (T*)h, d, (const WT*)w, width, eps);
     else
         thn_launch(rmsnorm_kernel<T, WT, false>, rows, kNormThreads, 0, stream, (T*)y, (T*)h, d, (const WT*)w, width, eps);
 }
 
-// y = RMSNorm(h).  With d (a tensor of h's type) or d_parts (n_parts float32 partials, each
-// rows * width): h is updated in place to rnd(h + d) first.
-THN_API int thn_rmsnorm(void* y, void* h, const void* d, const float* d_parts, int n_parts, const void* w, int rows,
-                        int width, float eps, int dtype, int w_dtype, cudaStream_t stream) {
+// y = RMSNorm(h).  With d (a tensor of h's type): h is updated in place to rnd(h + d) first.
+THN_API int thn_rmsnorm(void* y, void* h, const void* d, const void* w, int rows, int width, float eps, int dtype,
+                        int w_dtype, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", rows, width);
     THN_CHECK_ARG(eps > 0.f, "rmsnorm: eps must be positive, got %g", (double)eps);
-    THN_CHECK_ARG(!(d && d_parts) && (d_parts == nullptr || n_parts >= 1), "rmsnorm: one source for d, please");
     if (rows == 0) return THN_OK;
-    const bool add = d || d_parts;
-    const long long stride = (long long)rows * width;
     if (dtype == THN_F32 && w_dtype == THN_F32)
-        launch_rmsnorm<float, float>(y, h, Source<float>{(const float*)d, d_parts, n_parts, stride}, add, w, rows,
-                                     width, eps, stream);
+        launch_rmsnorm<float, float>(y, h, (const float*)d, w, rows, width, eps, stream);
     else if (dtype == THN_BF16 && w_dtype == THN_BF16 &&
-             launch_rmsnorm_vec<__nv_bfloat16>(y, h, d, d_parts, w, rows, width, eps, stream)) {
-    } else if (dtype == THN_BF16 && w_dtype == THN_F32 &&
-               launch_rmsnorm_vec<float>(y, h, d, d_parts, w, rows, width, eps, stream)) {
+             launch_rmsnorm_vec<__nv_bfloat16>(y, h, d, w, rows, width, eps, stream)) {
+    } else if (dtype == THN_BF16 && w_dtype == THN_F32 && launch_rmsnorm_vec<float>(y, h, d, w, rows, width, eps, stream)) {
     } else if (dtype == THN_BF16 && w_dtype == THN_BF16)
-        launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(
-            y, h, Source<__nv_bfloat16>{(const __nv_bfloat16*)d, d_parts, n_parts, stride}, add, w, rows, width, eps,
-            stream);
+        launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(y, h, (const __nv_bfloat16*)d, w, rows, width, eps, stream);
     else if (dtype == THN_BF16 && w_dtype == THN_F32)
-        launch_rmsnorm<__nv_bfloat16, float>(
-            y, h, Source<__nv_bfloat16>{(const __nv_bfloat16*)d, d_parts, n_parts, stride}, add, w, rows, width, eps,
-            stream);
+        launch_rmsnorm<__nv_bfloat16, float>(y, h, (const __nv_bfloat16*)d, w, rows, width, eps, stream);
     else
         THN_CHECK_ARG(false, "rmsnorm: unsupported dtypes activation=%d gain=%d", dtype, w_dtype);
     return thn_launch_status("rmsnorm");
@@ -232,15 +217,15 @@ THN_API int thn_rmsnorm(void* y, void* h, const void* d, const float* d_parts, i
 
 // out[m, i] = rnd(rnd(g / (1 + exp(-g))) * u), g = gu[m, i], u = gu[m, inter + i].
 template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, Source<T> gu, long long total, int inter) {
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int inter) {
     pdl_launch_dependents();
     pdl_wait();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
         const long long m = e / inter;
         const int i = (int)(e - m * inter);
-        const float g = gu.load(m * 2 * inter + i);
-        const float u = gu.load(m * 2 * inter + inter + i);
+        const float g = to_f32<T>(gu[m * 2 * inter + i]);
+        const float u = to_f32<T>(gu[m * 2 * inter + inter + i]);
         const float s = rnd<T>(g / (1.0f + expf(-g)));
         out[e] = from_f32<T>(s * u);
     }
@@ -276,59 +261,29 @@ __global__ void swiglu_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __
     }
 }
 
-// gu [rows, 2 * inter] as a tensor, or as n_parts float32 partials.
-THN_API int thn_swiglu(void* out, const void* gu, const float* gu_parts, int n_parts, int rows, int inter, int dtype,
-                       cudaStream_t stream) {
+// gu [rows, 2 * inter] (gate columns, then up columns) -> out [rows, inter].
+THN_API int thn_swiglu(void* out, const void* gu, int rows, int inter, int dtype, cudaStream_t stream) {
     THN_CHECK_ARG(rows >= 0 && inter > 0, "swiglu: bad sizes rows=%d inter=%d", rows, inter);
-    THN_CHECK_ARG((gu != nullptr) != (gu_parts != nullptr), "swiglu: one source, please");
     const long long total = (long long)rows * inter;
     if (total == 0) return THN_OK;
     const int threads = 256;
     const long long want = (total + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    const long long stride = 2 * total;
-    if (dtype == THN_BF16 && gu && inter % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    if (dtype == THN_BF16 && inter % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
         const long long vecs = total / 8;
         const long long want_vec = (vecs + threads - 1) / threads;
-        thn_launch(swiglu_bf16_vec_kernel, (unsigned)(want_vec < 148 * 32 ? want_vec : 148 * 32), threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, vecs, inter / 8);
+        thn_launch(swiglu_bf16_vec_kernel, (unsigned)(want_vec < 148 * 32 ? want_vec : 148 * 32), threads, 0, stream,
+                   (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, vecs, inter / 8);
         return thn_launch_status("swiglu");
     }
     if (dtype == THN_F32)
-        thn_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (float*)out, Source<float>{(const float*)gu, gu_parts, n_parts, stride}, total, inter);
+        thn_launch(swiglu_kernel<float>, blocks, threads, 0, stream, (float*)out, (const float*)gu, total, inter);
     else if (dtype == THN_BF16)
-        thn_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out, Source<__nv_bfloat16>{(const __nv_bfloat16*)gu, gu_parts, n_parts, stride}, total,
-            inter);
+        thn_launch(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gu, total, inter);
     else
         THN_CHECK_ARG(false, "swiglu: unknown dtype %d", dtype);
     return thn_launch_status("swiglu");
-}
-
-// ------------------------------------------------------------------ partial sums -> tensor
-
-template <typename T>
-__global__ void resolve_kernel(T* __restrict__ out, Source<T> src, long long total) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride)
-        out[e] = from_f32<T>(src.load(e));
-}
-
-// out[e] = rnd(sum over parts), e < total: what the product would have stored.
-THN_API int thn_resolve_parts(void* out, const float* parts, int n_parts, long long total, int dtype,
-                              cudaStream_t stream) {
-    THN_CHECK_ARG(total >= 0 && n_parts >= 1, "resolve_parts: bad sizes");
-    if (total == 0) return THN_OK;
-    const long long want = (total + 255) / 256;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    if (dtype == THN_F32)
-        thn_launch(resolve_kernel<float>, blocks, 256, 0, stream, (float*)out, Source<float>{nullptr, parts, n_parts, total},
-                                                          total);
-    else if (dtype == THN_BF16)
-        thn_launch(resolve_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, Source<__nv_bfloat16>{nullptr, parts, n_parts, total}, total);
-    else
-        THN_CHECK_ARG(false, "resolve_parts: unknown dtype %d", dtype);
-    return thn_launch_status("resolve_parts");
 }
 
 // ------------------------------------------------------------------ step bookkeeping

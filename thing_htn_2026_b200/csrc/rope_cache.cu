@@ -12,7 +12,7 @@ constexpr int kMaxHeadDim = 512;
 
 template <typename T, typename WT>
 __global__ void qk_norm_rope_cache_kernel(
-    T* __restrict__ q_out, Source<T> qkv, const WT* __restrict__ q_gain, const WT* __restrict__ k_gain,
+    T* __restrict__ q_out, const T* __restrict__ qkv, const WT* __restrict__ q_gain, const WT* __restrict__ k_gain,
     float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int table_len, int rotary_dim,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_rows, int n_q, int write_cache,
     int* __restrict__ err) {
@@ -45,14 +45,14 @@ __global__ void qk_norm_rope_cache_kernel(
     }
 
     if (!is_q && !is_k) {  // V: plain copy
-        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(qkv.load(src + d));
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(to_f32<T>(qkv[src + d]));
         return;
     }
 
     const WT* gain = is_q ? q_gain : k_gain;
     float ss = 0.f;
     for (int d = lane; d < D; d += 32) {
-        const float v = qkv.load(src + d);
+        const float v = to_f32<T>(qkv[src + d]);
         buf[d] = v;
         ss += v * v;
     }
@@ -335,8 +335,7 @@ __global__ void qk_norm_rope_cache_bf16_vec_kernel(
 // qkv [n_rows, (n_q + 2*n_kv) * head_dim] -> q_out [n_rows, n_q * head_dim]; K and V of
 // every row go to (slot, position) of the cache entry unless write_cache == 0.
 // q_gain/k_gain may be null (no head norm); cos_tab may be null (no rotation).
-// qkv comes as a tensor, or as qkv_n_parts float32 split-K partials.
-THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qkv_parts, int qkv_n_parts,
+THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv,
                                    const void* q_gain, const void* k_gain, int w_dtype,
                                    float eps, const float* cos_tab, const float* sin_tab, int table_len,
                                    int rotary_dim, const int* row_slot, const int* row_pos, void* kv_base,
@@ -348,15 +347,14 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
     THN_CHECK_ARG(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                   "qk_norm_rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
     THN_CHECK_ARG((q_gain == nullptr) == (k_gain == nullptr), "qk_norm_rope_cache: q and k gains come together");
-    THN_CHECK_ARG((qkv != nullptr) != (qkv_parts != nullptr), "qk_norm_rope_cache: one source for qkv, please");
+    THN_CHECK_ARG(qkv != nullptr, "qk_norm_rope_cache: no q/k/v rows");
     if (n_rows == 0) return THN_OK;
     PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
     const int warps = 4;
     const long long units = (long long)n_rows * (n_q + 2 * n_kv);
     const unsigned blocks = (unsigned)((units + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
-    const long long part_stride = (long long)n_rows * (n_q + 2 * n_kv) * head_dim;
-    if (dtype == THN_BF16 && qkv && q_gain && cos_tab && rotary_dim == head_dim &&
+    if (dtype == THN_BF16 && q_gain && cos_tab && rotary_dim == head_dim &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
         const bool many = n_rows > kFewRows && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kv_base |
                                                   (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos_tab |
@@ -388,7 +386,7 @@ THN_API int thn_qk_norm_rope_cache(void* q_out, const void* qkv, const float* qk
     }
 #define LAUNCH(T, WT)                                                                                              \
     thn_launch(qk_norm_rope_cache_kernel<T, WT>, blocks, warps * 32, smem, stream, \
-        (T*)q_out, Source<T>{(const T*)qkv, qkv_parts, qkv_n_parts, part_stride}, (const WT*)q_gain,               \
+        (T*)q_out, (const T*)qkv, (const WT*)q_gain,                                                                \
         (const WT*)k_gain, eps, cos_tab, sin_tab, table_len,                                                       \
         rotary_dim, row_slot, row_pos, kv, n_rows, n_q, write_cache, err)
     if (dtype == THN_F32 && w_dtype == THN_F32) LAUNCH(float, float);

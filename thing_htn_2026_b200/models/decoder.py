@@ -98,7 +98,7 @@ class DecoderModel:
         ``err``: the step's device error word."""
         if rows is not None:
             h = ops.gather_rows(h, rows)
-            d = ops.gather_rows(ops.resolve(d), rows) if d is not None else None
+            d = ops.gather_rows(d, rows) if d is not None else None
         n = self.final_norm.forward(h) if d is None else self.final_norm.add_forward(h, d)
         return self.head.forward(n, err)
 

@@ -36,10 +36,8 @@ class KernelError(RuntimeError):
 
 _SIGNATURES = {
     "thn_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "thn_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_int,
-                    c_void_p],
-    "thn_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "thn_resolve_parts": [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p],
+    "thn_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "thn_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "thn_gemm_tcgen05_supported": [c_int, c_int, c_int],
     "thn_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_stream_supported": [c_int, c_int, c_int],
@@ -49,7 +47,7 @@ _SIGNATURES = {
     "thn_step_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_advance": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_rope_table": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+    "thn_qk_norm_rope_cache": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                                c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_attention_decode_fused_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
@@ -215,46 +213,6 @@ def gather_rows(table: torch.Tensor, index: torch.Tensor, err: Optional[torch.Te
     return out
 
 
-@dataclass
-class SplitSum:
-    """The output of a matrix product as split-K partial sums: ``parts`` is float32
-    ``[n_parts, rows, width]`` and the product is their sum over the first axis, rounded to
-    ``dtype``.  Kernels that consume a product take this in place of a tensor and do the
-    sum themselves; :func:`resolve` turns it into a tensor."""
-
-    parts: torch.Tensor
-    dtype: torch.dtype
-
-    @property
-    def shape(self):
-        return self.parts.shape[1:]
-
-
-Product = "torch.Tensor | SplitSum"
-
-
-def _source(value, what: str, dtype: torch.dtype):
-    """(tensor pointer, parts pointer, n_parts) of a product given either way."""
-    if isinstance(value, SplitSum):
-        if value.dtype != dtype:
-            raise KernelError(f"{what}: product is {value.dtype}, expected {dtype}")
-        _need(value.parts, what, torch.float32)
-        return None, _ptr(value.parts), value.parts.shape[0]
-    _need(value, what, dtype)
-    return _ptr(value), None, 0
-
-
-def resolve(value) -> torch.Tensor:
-    """A product as a tensor of its dtype (sums the partials if it came split)."""
-    if not isinstance(value, SplitSum):
-        return value
-    rows, width = value.shape
-    out = torch.empty((rows, width), dtype=value.dtype, device=value.parts.device)
-    _call("thn_resolve_parts", _ptr(out), _ptr(value.parts), value.parts.shape[0], rows * width,
-          DTYPE_CODE[value.dtype], _stream())
-    return out
-
-
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
     _need(x, "rmsnorm x")
     _need(gain, "rmsnorm gain")
@@ -262,35 +220,33 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
         raise KernelError(f"rmsnorm: gain has {gain.shape[0]} entries, rows have {x.shape[-1]}")
     y = torch.empty_like(x)
     rows = x.numel() // x.shape[-1]
-    _call("thn_rmsnorm", _ptr(y), _ptr(x), None, None, 0, _ptr(gain), rows, x.shape[-1], float(eps),
+    _call("thn_rmsnorm", _ptr(y), _ptr(x), None, _ptr(gain), rows, x.shape[-1], float(eps),
           _code(x, "rmsnorm"), _code(gain, "rmsnorm gain"), _stream())
     return y
 
 
-def add_rmsnorm(h: torch.Tensor, d, gain: torch.Tensor, eps: float) -> torch.Tensor:
-    """h <- round(h + d) in place; returns RMSNorm(h) * gain.  ``d`` is a tensor or a SplitSum."""
+def add_rmsnorm(h: torch.Tensor, d: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """h <- round(h + d) in place; returns RMSNorm(h) * gain."""
     _need(h, "add_rmsnorm h")
+    _need(d, "add_rmsnorm d", h.dtype)
     _need(gain, "add_rmsnorm gain")
     if tuple(d.shape) != tuple(h.shape) or gain.shape[0] != h.shape[-1]:
         raise KernelError(f"add_rmsnorm: shapes h {tuple(h.shape)}, d {tuple(d.shape)}, gain {tuple(gain.shape)}")
-    direct, parts, n_parts = _source(d, "add_rmsnorm d", h.dtype)
     y = torch.empty_like(h)
     rows = h.numel() // h.shape[-1]
-    _call("thn_rmsnorm", _ptr(y), _ptr(h), direct, parts, n_parts, _ptr(gain), rows, h.shape[-1], float(eps),
+    _call("thn_rmsnorm", _ptr(y), _ptr(h), _ptr(d), _ptr(gain), rows, h.shape[-1], float(eps),
           _code(h, "add_rmsnorm"), _code(gain, "add_rmsnorm gain"), _stream())
     return y
 
 
-def swiglu(gu) -> torch.Tensor:
-    """gu [rows, 2*I] (gate columns first; a tensor or a SplitSum) -> silu(gate) * up, [rows, I]."""
+def swiglu(gu: torch.Tensor) -> torch.Tensor:
+    """gu [rows, 2*I] (gate columns first) -> silu(gate) * up, [rows, I]."""
+    _need(gu, "swiglu")
     rows, width = gu.shape
     if width % 2:
         raise KernelError(f"swiglu: width {width} is odd")
-    dtype = gu.dtype
-    direct, parts, n_parts = _source(gu, "swiglu", dtype)
-    device = gu.parts.device if isinstance(gu, SplitSum) else gu.device
-    out = torch.empty((rows, width // 2), dtype=dtype, device=device)
-    _call("thn_swiglu", _ptr(out), direct, parts, n_parts, rows, width // 2, DTYPE_CODE[dtype], _stream())
+    out = torch.empty((rows, width // 2), dtype=gu.dtype, device=gu.device)
+    _call("thn_swiglu", _ptr(out), _ptr(gu), rows, width // 2, _code(gu, "swiglu"), _stream())
     return out
 
 
@@ -452,16 +408,16 @@ class RotaryTables:
 def qk_norm_rope_cache(qkv, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
                        eps: float, rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int,
                        write_cache: bool, err: torch.Tensor) -> torch.Tensor:
-    """qkv (a tensor or a SplitSum) -> q, normalised and rotated; K and V go to the cache."""
+    """qkv -> q, normalised and rotated; K and V go to the cache."""
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
     if tuple(qkv.shape) != (rows.n_rows, width):
         raise KernelError(f"qk_norm_rope_cache: qkv is {tuple(qkv.shape)}, expected {(rows.n_rows, width)}")
     if kv.storage.dtype != qkv.dtype:
         raise KernelError(f"qk_norm_rope_cache: cache is {kv.storage.dtype}, activations {qkv.dtype}")
-    direct, parts, n_parts = _source(qkv, "qk_norm_rope_cache qkv", qkv.dtype)
+    _need(qkv, "qk_norm_rope_cache qkv")
     q = torch.empty((rows.n_rows, n_q * kv.head_dim), dtype=qkv.dtype, device=kv.storage.device)
     w_code = _code(q_gain, "qk gains") if q_gain is not None else DTYPE_CODE[qkv.dtype]
-    _call("thn_qk_norm_rope_cache", _ptr(q), direct, parts, n_parts, _ptr(q_gain), _ptr(k_gain), w_code, float(eps),
+    _call("thn_qk_norm_rope_cache", _ptr(q), _ptr(qkv), _ptr(q_gain), _ptr(k_gain), w_code, float(eps),
           _ptr(rotary.cos) if rotary else None, _ptr(rotary.sin) if rotary else None,
           rotary.cos.shape[0] if rotary else 0, rotary.rotary_dim if rotary else 0,
           _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
@@ -568,7 +524,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     cache write and attention over the cache.  One kernel for single-token steps in bfloat16
     with head norm and full rotation at the tensor-core kernel's sizes; otherwise
     :func:`qk_norm_rope_cache` followed by :func:`attention`."""
-    fusable = (FUSE_DECODE_ATTENTION and rows.max_q_len == 1 and isinstance(qkv, torch.Tensor)
+    fusable = (FUSE_DECODE_ATTENTION and rows.max_q_len == 1
                and qkv.dtype == torch.bfloat16 and q_gain is not None and k_gain is not None and rotary is not None
                and rotary.rotary_dim == kv.head_dim and kv.storage.dtype == torch.bfloat16
                and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv))
@@ -633,7 +589,7 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 
 __all__ = [
-    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "SplitSum", "StepRows", "linear_stream", "linear_swiglu", "linear_tcgen05", "resolve", "add_rmsnorm", "advance",
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]
