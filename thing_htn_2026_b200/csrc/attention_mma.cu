@@ -301,48 +301,55 @@ __device__ __forceinline__ float gain_at(const void* gain, int f32, int i) {
     return f32 ? reinterpret_cast<const float*>(gain)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(gain)[i]);
 }
 
-// One head of D values, a lane holding [d0, d0 + E) and [D/2 + d0, ..): RMSNorm with gain,
-// then the rotation by the row's angles; every product rounded to bfloat16 as the reference does.
+// One head of D values, a lane holding [d0, d0 + E) and [D/2 + d0, ..) of it in registers:
+// RMSNorm with gain, then the rotation by the row's angles; every product rounded to bfloat16
+// as the reference does.
 template <int D>
-__device__ __forceinline__ void norm_rotate_head(const __nv_bfloat16* __restrict__ src, const void* gain, int gain_f32,
-                                                 float eps, const float (&c)[D / 64], const float (&sn)[D / 64], int lane,
+__device__ __forceinline__ void norm_rotate_head(const __nv_bfloat16 (&in_lo)[D / 64], const __nv_bfloat16 (&in_hi)[D / 64],
+                                                 const float (&g_lo)[D / 64], const float (&g_hi)[D / 64], float eps,
+                                                 const float (&c)[D / 64], const float (&sn)[D / 64],
                                                  __nv_bfloat16 (&lo)[D / 64], __nv_bfloat16 (&hi)[D / 64]) {
     using B = __nv_bfloat16;
-    constexpr int E = D / 64, kHalf = D / 2;
-    const int d0 = lane * E;
+    constexpr int E = D / 64;
     float a[E], b[E], ss = 0.f;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-        a[e] = __bfloat162float(src[d0 + e]);
-        b[e] = __bfloat162float(src[kHalf + d0 + e]);
+        a[e] = __bfloat162float(in_lo[e]);
+        b[e] = __bfloat162float(in_hi[e]);
         ss += a[e] * a[e] + b[e] * b[e];
     }
     ss = warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-        const float x0 = rnd<B>(gain_at(gain, gain_f32, d0 + e) * rnd<B>(a[e] * rstd));
-        const float x1 = rnd<B>(gain_at(gain, gain_f32, kHalf + d0 + e) * rnd<B>(b[e] * rstd));
+        const float x0 = rnd<B>(g_lo[e] * rnd<B>(a[e] * rstd));
+        const float x1 = rnd<B>(g_hi[e] * rnd<B>(b[e] * rstd));
         lo[e] = __float2bfloat16_rn(rnd<B>(x0 * c[e]) + rnd<B>(-x1 * sn[e]));
         hi[e] = __float2bfloat16_rn(rnd<B>(x1 * c[e]) + rnd<B>(x0 * sn[e]));
     }
 }
 
 // CLUSTER: the splits of one (sequence, kv head) are the blocks of one thread-block cluster,
-// and their partial results meet in distributed shared memory instead of global memory:
-// every block parks its partial in its own shared memory, the cluster's hardware barrier
-// orders it, block 0 reads all of them, combines them in split order and writes the output;
-// a second barrier keeps every block's shared memory alive until block 0 has read it.
+// and their partial results meet in distributed shared memory instead of global memory: after
+// a first barrier (every block is done with its tile buffers) each block writes its partial
+// into block 0's tile buffers, a second barrier orders that, and block 0 combines the
+// partials in split order from its own shared memory and writes the output.
+// 2^x on the special-function unit (about two float32 ulp).  Used for the weights with which
+// partial results are merged: the same weight scales a partial's sum and its output.
+__device__ __forceinline__ float merge_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
-__device__ __forceinline__ float load_from_block(const float* mine, uint32_t rank) {
+// *mine as it lies in block `rank` of the cluster <- v
+__device__ __forceinline__ void store_to_block(float* mine, uint32_t rank, float v) {
     uint32_t local = (uint32_t)__cvta_generic_to_shared(mine), remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
 template <int D, int STAGES, bool FUSED, bool CLUSTER>
@@ -354,6 +361,44 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     pdl_launch_dependents();
     pdl_wait();
     constexpr int kPitch = D + 8, kStages = STAGES;
+    constexpr int E = D / 64, kHalf = D / 2;
+    // FUSED: the step's raw rows and the gains are requested first, so that they travel while
+    // the block finds its pages (position -> page -> tile is a chain of dependent loads).
+    __nv_bfloat16 raw_lo[4][E], raw_hi[4][E];              // query heads warp, warp + 4, warp + 8, warp + 12 of the group
+    __nv_bfloat16 raw_k_lo[E], raw_k_hi[E], new_v_lo[E], new_v_hi[E];   // warp 0: the step's own key and value
+    float qg_lo[E], qg_hi[E], kg_lo[E], kg_hi[E];
+    if (FUSED) {
+        const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5, d0 = lane_ * E;
+        const int G_ = n_q / kv.n_kv;
+        const __nv_bfloat16* row = fused.qkv + (size_t)blockIdx.x * (n_q + 2 * kv.n_kv) * D;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp_ + 4 * i;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                raw_lo[i][e] = r < G_ ? row[(size_t)(blockIdx.y * G_ + r) * D + d0 + e] : __float2bfloat16_rn(0.f);
+                raw_hi[i][e] = r < G_ ? row[(size_t)(blockIdx.y * G_ + r) * D + kHalf + d0 + e] : __float2bfloat16_rn(0.f);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            qg_lo[e] = gain_at(fused.q_gain, fused.gain_f32, d0 + e);
+            qg_hi[e] = gain_at(fused.q_gain, fused.gain_f32, kHalf + d0 + e);
+        }
+        if (warp_ == 0 && fused.write_cache) {
+            const __nv_bfloat16* k_row = row + (size_t)(n_q + blockIdx.y) * D;
+            const __nv_bfloat16* v_row = row + (size_t)(n_q + kv.n_kv + blockIdx.y) * D;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                raw_k_lo[e] = k_row[d0 + e];
+                raw_k_hi[e] = k_row[kHalf + d0 + e];
+                new_v_lo[e] = v_row[d0 + e];
+                new_v_hi[e] = v_row[kHalf + d0 + e];
+                kg_lo[e] = gain_at(fused.k_gain, fused.gain_f32, d0 + e);
+                kg_hi[e] = gain_at(fused.k_gain, fused.gain_f32, kHalf + d0 + e);
+            }
+        }
+    }
     __shared__ int is_last;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [16][kPitch]
@@ -374,8 +419,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     const int t_begin = t_first + split * per_split;
     const int t_end = min(t_begin + per_split, t_last + 1);      // exclusive; may be <= t_begin (empty split)
 
-    constexpr int E = D / 64, kHalf = D / 2;
-    __nv_bfloat16 new_k_lo[E], new_k_hi[E], new_v_lo[E], new_v_hi[E];      // warp 0, FUSED: the step's own key and value
+    __nv_bfloat16 new_k_lo[E], new_k_hi[E];
     const bool patches = FUSED && fused.write_cache && t_begin <= t_last && t_last < t_end;
     if (!FUSED) {
         for (int c = threadIdx.x; c < 16 * (D / 8); c += kThreads) {
@@ -418,12 +462,12 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             c[e] = rnd<__nv_bfloat16>(fused.cos_tab[(size_t)pos * kHalf + d0 + e]);
             sn[e] = rnd<__nv_bfloat16>(fused.sin_tab[(size_t)pos * kHalf + d0 + e]);
         }
-        const __nv_bfloat16* row = fused.qkv + (size_t)b * (n_q + 2 * kv.n_kv) * D;
-        for (int r = warp; r < 16; r += kThreads / 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp + 4 * i;
             __nv_bfloat16 lo[E], hi[E];
-            if (r < G) {
-                norm_rotate_head<D>(row + (size_t)(kvh * G + r) * D, fused.q_gain, fused.gain_f32, fused.eps, c, sn, lane,
-                                    lo, hi);
+            if (r < G) {                                   // the same for the whole warp
+                norm_rotate_head<D>(raw_lo[i], raw_hi[i], qg_lo, qg_hi, fused.eps, c, sn, lo, hi);
             } else {
 #pragma unroll
                 for (int e = 0; e < E; ++e) lo[e] = hi[e] = __float2bfloat16_rn(0.f);
@@ -434,16 +478,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
                 q_smem[r * kPitch + kHalf + d0 + e] = hi[e];
             }
         }
-        if (patches && warp == 0) {
-            norm_rotate_head<D>(row + (size_t)(n_q + kvh) * D, fused.k_gain, fused.gain_f32, fused.eps, c, sn, lane,
-                                new_k_lo, new_k_hi);
-            const __nv_bfloat16* v_row = row + (size_t)(n_q + kv.n_kv + kvh) * D;
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-                new_v_lo[e] = v_row[d0 + e];
-                new_v_hi[e] = v_row[kHalf + d0 + e];
-            }
-        }
+        if (patches && warp == 0) norm_rotate_head<D>(raw_k_lo, raw_k_hi, kg_lo, kg_hi, fused.eps, c, sn, new_k_lo, new_k_hi);
     }
     if (kStages == 3) cp_async_wait<2>(); else cp_async_wait<1>();          // Q has landed
     __syncthreads();
@@ -510,10 +545,14 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     cp_async_wait<0>();
     __syncthreads();
 
-    // Merge the four warps through shared memory (the tile buffers are free now).
+    // Merge the four warps through shared memory (the tile buffers are free now).  Only the G
+    // rows that are query heads are kept; a row takes D + 8 floats so that the rows a warp
+    // stores together fall into different banks.
+    constexpr int kOPitch = D + 8;
+    constexpr int kKeep = 16 * D / kThreads;                    // merged values a thread holds (G <= 16)
     float* m_smem = reinterpret_cast<float*>(k_smem);           // [4][16]
     float* l_smem = m_smem + 64;                                // [4][16]
-    float* o_smem = l_smem + 64;                                // [4][16][D]
+    float* o_smem = l_smem + 64;                                // [4][G][kOPitch]
     const int g = lane >> 2;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -521,82 +560,110 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = g + 8 * r;
-        if (tq == 0) {
-            m_smem[warp * 16 + row] = st.m[r];
-            l_smem[warp * 16 + row] = l;
-        }
+        if (row < G) {
+            if (tq == 0) {
+                m_smem[warp * 16 + row] = st.m[r];
+                l_smem[warp * 16 + row] = l;
+            }
 #pragma unroll
-        for (int nd = 0; nd < D / 8; ++nd) {
-            o_smem[(warp * 16 + row) * D + nd * 8 + tq * 2] = o[nd][2 * r];
-            o_smem[(warp * 16 + row) * D + nd * 8 + tq * 2 + 1] = o[nd][2 * r + 1];
+            for (int nd = 0; nd < D / 8; ++nd)
+                *reinterpret_cast<float2*>(o_smem + (warp * G + row) * kOPitch + nd * 8 + tq * 2) =
+                    make_float2(o[nd][2 * r], o[nd][2 * r + 1]);
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < G * D; e += kThreads) {
-        const int row = e / D, d = e % D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, m_smem[w * 16 + row]);
-        float l = 0.f, acc = 0.f;
-        if (m != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float wgt = exp2f(m_smem[w * 16 + row] - m);
-                l += l_smem[w * 16 + row] * wgt;
-                acc += o_smem[(w * 16 + row) * D + d] * wgt;
+    // weight of warp w in row r, and the row's (max, sum), once: threads 0 .. 4 G - 1
+    float* wgt_smem = o_smem + 4 * 16 * kOPitch;                // [16][4]; then (max, sum) [16][2]
+    float* ml_smem = wgt_smem + 64;
+    if ((threadIdx.x & ~31) < 4 * G) {                          // whole warps: the shuffles below take all 32 lanes
+        const bool live = threadIdx.x < 4 * G;
+        const int row = min((int)threadIdx.x >> 2, 15), w = threadIdx.x & 3;
+        const float mine = m_smem[w * 16 + row];
+        float m = mine;
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        const float wgt = m == -INFINITY ? 0.f : merge_exp2(mine - m);
+        float l = l_smem[w * 16 + row] * wgt;
+        const float l1 = l + __shfl_xor_sync(0xffffffffu, l, 1);          // (w0 + w1), (w2 + w3): the order is fixed
+        l = l1 + __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (live) {
+            wgt_smem[row * 4 + w] = wgt;
+            if (w == 0) {
+                ml_smem[row * 2] = m;
+                ml_smem[row * 2 + 1] = l;
             }
         }
+    }
+    __syncthreads();
+    float keep[kKeep];
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+        const int e = threadIdx.x + i * kThreads;
+        keep[i] = 0.f;
+        if (e >= G * D) continue;
+        const int row = e / D, d = e % D;
+        const float4 wgt = *reinterpret_cast<const float4*>(wgt_smem + row * 4);
+        const float acc = (o_smem[(0 * G + row) * kOPitch + d] * wgt.x + o_smem[(1 * G + row) * kOPitch + d] * wgt.y) +
+                          (o_smem[(2 * G + row) * kOPitch + d] * wgt.z + o_smem[(3 * G + row) * kOPitch + d] * wgt.w);
         const size_t head = (size_t)b * n_q + kvh * G + row;
         if (n_splits == 1) {
-            out[head * D + d] = __float2bfloat16_rn(acc / l);
+            out[head * D + d] = __float2bfloat16_rn(acc / ml_smem[row * 2 + 1]);
         } else if (CLUSTER) {
-            float* stage_ml = reinterpret_cast<float*>(v_smem) + 16 * 32 + 16;     // [16][2], then [16][D]
-            stage_ml[32 + e] = acc;
-            if (d == 0) {
-                stage_ml[row * 2] = m;
-                stage_ml[row * 2 + 1] = l;
-            }
+            keep[i] = acc;
         } else {
             __stcg(part_o + (head * n_splits + split) * D + d, acc);
             if (d == 0) {
-                __stcg(part_ml + (head * n_splits + split) * 2, m);
-                __stcg(part_ml + (head * n_splits + split) * 2 + 1, l);
+                __stcg(part_ml + (head * n_splits + split) * 2, ml_smem[row * 2]);
+                __stcg(part_ml + (head * n_splits + split) * 2 + 1, ml_smem[row * 2 + 1]);
             }
         }
     }
     if (CLUSTER) {
-        // no early return above in this mode: every thread of every block reaches both barriers
-        cluster_sync_all();
-        if (split == 0 && n_splits > 1) {
-            const float* stage_ml = reinterpret_cast<const float*>(v_smem) + 16 * 32 + 16;
-            float* w_smem = reinterpret_cast<float*>(v_smem);            // [16][32]
-            float* l_total = w_smem + 16 * 32;                           // [16]
-            for (int row = warp; row < G; row += 4) {
-                const float ms = lane < n_splits ? load_from_block(stage_ml + row * 2, (uint32_t)lane) : -INFINITY;
-                const float ls = lane < n_splits ? load_from_block(stage_ml + row * 2 + 1, (uint32_t)lane) : 0.f;
-                const float m = warp_max(ms);
-                const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - m);
-                const float l = warp_sum(ls * wgt);
-                w_smem[row * 32 + lane] = wgt;
-                if (lane == 0) l_total[row] = l;
-            }
-            __syncthreads();
-            for (int e = threadIdx.x; e < G * D; e += kThreads) {
-                const int row = e / D, d = e % D;
-                const size_t head = (size_t)b * n_q + kvh * G + row;
-                float acc = 0.f;
-                for (int s0 = 0; s0 < n_splits; s0 += 8) {                // eight loads in flight, added in split order
-                    float v[8];
+        // No early return above in this mode: every thread of every block reaches both barriers.
+        // In block 0, over the tile buffers: after each block's own (max, sum) of its warps, the
+        // partial outputs [split][G * D]; near the end (max, sum) [8 splits][16 rows][2] and the
+        // weights of the splits.
+        constexpr int kTileFloats = 2 * kStages * kTile * kPitch / 2;
+        float* recv_o = reinterpret_cast<float*>(k_smem) + 128;
+        float* w_smem = reinterpret_cast<float*>(k_smem) + kTileFloats - (16 * 32 + 16);     // [16][32]
+        float* l_total = w_smem + 16 * 32;                       // [16]
+        float* recv_ml = w_smem - 8 * 32;
+        // (the row's (max, sum) leave this block's buffers before block 0's copy of them may be overwritten)
+        const float ml_held = threadIdx.x < 2 * G ? ml_smem[threadIdx.x] : 0.f;
+        cluster_sync_all();                                      // every block is done with its tile buffers
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        v[j] = s0 + j < n_splits ? load_from_block(stage_ml + 32 + e, (uint32_t)(s0 + j)) : 0.f;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc += v[j] * w_smem[row * 32 + ((s0 + j) & 31)];
-                }
-                out[head * D + d] = __float2bfloat16_rn(acc / l_total[row]);
-            }
+        for (int i = 0; i < kKeep; ++i) {
+            const int e = threadIdx.x + i * kThreads;
+            if (e >= G * D) continue;
+            store_to_block(recv_o + split * G * D + e, 0, keep[i]);
         }
-        cluster_sync_all();
+        if (threadIdx.x < 2 * G) store_to_block(recv_ml + split * 32 + threadIdx.x, 0, ml_held);
+        cluster_sync_all();                                      // every partial is in block 0
+        if (split != 0) return;
+        for (int row = warp; row < G; row += 4) {
+            const float ms = lane < n_splits ? recv_ml[lane * 32 + row * 2] : -INFINITY;
+            const float ls = lane < n_splits ? recv_ml[lane * 32 + row * 2 + 1] : 0.f;
+            const float m = warp_max(ms);
+            const float wgt = ms == -INFINITY ? 0.f : merge_exp2(ms - m);
+            const float l = warp_sum(ls * wgt);
+            w_smem[row * 32 + lane] = wgt;
+            if (lane == 0) l_total[row] = 1.0f / l;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kKeep; ++i) {
+            const int e = threadIdx.x + i * kThreads;
+            if (e >= G * D) continue;
+            const int row = e / D, d = e % D;
+            const size_t head = (size_t)b * n_q + kvh * G + row;
+            float v[8];                                          // at most 8 splits in a cluster
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = j < n_splits ? recv_o[j * G * D + e] : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc += v[j] * w_smem[row * 32 + j];                 // split order
+            out[head * D + d] = __float2bfloat16_rn(acc * l_total[row]);
+        }
         return;
     }
     if (n_splits == 1 || counters == nullptr) return;

@@ -487,6 +487,8 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128) -> int:
     """Splits of the key range per (sequence, kv head) so that a single-token step fills the
     GPU with one wave of blocks.  It depends on the batch only, never on the lengths, so a captured
     step stays valid while the sequences grow."""
+    if os.environ.get("THN_DECODE_SPLITS"):
+        return int(os.environ["THN_DECODE_SPLITS"])
     capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
     most = lib().thn_attention_decode_cluster_splits() or 16      # a cluster holds at most 8 blocks
     return max(1, min(most, capacity // max(1, n_seqs * n_kv)))
