@@ -445,6 +445,16 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         }
         cp_async_commit();
     };
+    // FUSED: the row's angles are requested before the page of the first tile is looked up
+    float angle_c[E], angle_s[E];
+    if (FUSED) {
+        const int at = pos < fused.table_len ? pos : 0;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            angle_c[e] = fused.cos_tab[(size_t)at * kHalf + lane * E + e];
+            angle_s[e] = fused.sin_tab[(size_t)at * kHalf + lane * E + e];
+        }
+    }
     issue(t_begin, 0);
     if (kStages == 3) issue(t_begin + 1, 1);
 
@@ -459,8 +469,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         float c[E], sn[E];
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            c[e] = rnd<__nv_bfloat16>(fused.cos_tab[(size_t)pos * kHalf + d0 + e]);
-            sn[e] = rnd<__nv_bfloat16>(fused.sin_tab[(size_t)pos * kHalf + d0 + e]);
+            c[e] = rnd<__nv_bfloat16>(angle_c[e]);
+            sn[e] = rnd<__nv_bfloat16>(angle_s[e]);
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
