@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     constexpr int E = D / 64, kHalf = D / 2;
     // FUSED: the step's raw rows and the gains are requested first, so that they travel while
     // the block finds its pages (position -> page -> tile is a chain of dependent loads).
-    __nv_bfloat16 raw_lo[4][E], raw_hi[4][E];              // query heads warp, warp + 4, warp + 8, warp + 12 of the group
+    __nv_bfloat16 raw_lo[E], raw_hi[E];                    // query head `warp` of the group (heads warp + 4, .. are read later)
     __nv_bfloat16 raw_k_lo[E], raw_k_hi[E], new_v_lo[E], new_v_hi[E];   // warp 0: the step's own key and value
     float qg_lo[E], qg_hi[E], kg_lo[E], kg_hi[E];
     if (FUSED) {
@@ -372,13 +372,9 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         const int G_ = n_q / kv.n_kv;
         const __nv_bfloat16* row = fused.qkv + (size_t)blockIdx.x * (n_q + 2 * kv.n_kv) * D;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = warp_ + 4 * i;
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-                raw_lo[i][e] = r < G_ ? row[(size_t)(blockIdx.y * G_ + r) * D + d0 + e] : __float2bfloat16_rn(0.f);
-                raw_hi[i][e] = r < G_ ? row[(size_t)(blockIdx.y * G_ + r) * D + kHalf + d0 + e] : __float2bfloat16_rn(0.f);
-            }
+        for (int e = 0; e < E; ++e) {
+            raw_lo[e] = warp_ < G_ ? row[(size_t)(blockIdx.y * G_ + warp_) * D + d0 + e] : __float2bfloat16_rn(0.f);
+            raw_hi[e] = warp_ < G_ ? row[(size_t)(blockIdx.y * G_ + warp_) * D + kHalf + d0 + e] : __float2bfloat16_rn(0.f);
         }
 #pragma unroll
         for (int e = 0; e < E; ++e) {
@@ -472,12 +468,19 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             c[e] = rnd<__nv_bfloat16>(angle_c[e]);
             sn[e] = rnd<__nv_bfloat16>(angle_s[e]);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = warp + 4 * i;
+        const __nv_bfloat16* qkv_row = fused.qkv + (size_t)b * (n_q + 2 * kv.n_kv) * D;
+#pragma unroll 1
+        for (int r = warp; r < 16; r += 4) {              // rolled: one pass per warp when G <= 4
             __nv_bfloat16 lo[E], hi[E];
             if (r < G) {                                   // the same for the whole warp
-                norm_rotate_head<D>(raw_lo[i], raw_hi[i], qg_lo, qg_hi, fused.eps, c, sn, lo, hi);
+                if (r != warp) {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        raw_lo[e] = qkv_row[(size_t)(kvh * G + r) * D + d0 + e];
+                        raw_hi[e] = qkv_row[(size_t)(kvh * G + r) * D + kHalf + d0 + e];
+                    }
+                }
+                norm_rotate_head<D>(raw_lo, raw_hi, qg_lo, qg_hi, fused.eps, c, sn, lo, hi);
             } else {
 #pragma unroll
                 for (int e = 0; e < E; ++e) lo[e] = hi[e] = __float2bfloat16_rn(0.f);
@@ -605,12 +608,13 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         }
     }
     __syncthreads();
+    // (These loops run once per block and are left rolled on purpose: unrolled, their
+    // instructions cost more to fetch than to execute.)
     float keep[kKeep];
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < kKeep; ++i) {
         const int e = threadIdx.x + i * kThreads;
-        keep[i] = 0.f;
-        if (e >= G * D) continue;
+        if (e >= G * D) break;
         const int row = e / D, d = e % D;
         const float4 wgt = *reinterpret_cast<const float4*>(wgt_smem + row * 4);
         const float acc = (o_smem[(0 * G + row) * kOPitch + d] * wgt.x + o_smem[(1 * G + row) * kOPitch + d] * wgt.y) +
@@ -641,10 +645,10 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         // (the row's (max, sum) leave this block's buffers before block 0's copy of them may be overwritten)
         const float ml_held = threadIdx.x < 2 * G ? ml_smem[threadIdx.x] : 0.f;
         cluster_sync_all();                                      // every block is done with its tile buffers
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < kKeep; ++i) {
             const int e = threadIdx.x + i * kThreads;
-            if (e >= G * D) continue;
+            if (e >= G * D) break;
             store_to_block(recv_o + split * G * D + e, 0, keep[i]);
         }
         if (threadIdx.x < 2 * G) store_to_block(recv_ml + split * 32 + threadIdx.x, 0, ml_held);
@@ -660,10 +664,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             if (lane == 0) l_total[row] = 1.0f / l;
         }
         __syncthreads();
-#pragma unroll
-        for (int i = 0; i < kKeep; ++i) {
-            const int e = threadIdx.x + i * kThreads;
-            if (e >= G * D) continue;
+#pragma unroll 1
+        for (int e = threadIdx.x; e < G * D; e += kThreads) {
             const int row = e / D, d = e % D;
             const size_t head = (size_t)b * n_q + kvh * G + row;
             float v[8];                                          // at most 8 splits in a cluster
