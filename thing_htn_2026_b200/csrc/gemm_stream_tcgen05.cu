@@ -535,9 +535,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
             }
         }
         // column j goes to block j % n_ranks, as that block's column j / n_ranks, sender `rank`
+        int owner = 0, slot = rank;                 // slot = (j / n_ranks) * n_ranks + rank, kept without divisions
 #pragma unroll
-        for (int j = 0; j < NX; ++j)
-            if (j < M) store_to_block(recv + ((j / n_ranks) * n_ranks + rank) * BW + r, (uint32_t)(j % n_ranks), acc[j]);
+        for (int j = 0; j < NX; ++j) {
+            if (j < M) store_to_block(recv + slot * BW + r, (uint32_t)owner, acc[j]);
+            if (++owner == n_ranks) {
+                owner = 0;
+                slot += n_ranks;
+            }
+        }
     }
     cluster_sync();
     if (warp >= 2) {
