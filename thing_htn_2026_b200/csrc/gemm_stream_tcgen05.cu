@@ -189,16 +189,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
     const long long u_begin = (long long)blockIdx.x * span;
     const long long u_end = min(u_begin + span, total_units);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < S::kStages; ++s) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, 1);
-        }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(acc_full + i, 1);
-            mbar_init(acc_empty + i, 4);       // one arrival per epilogue warp
-        }
-        *give_up = 0;
+    if (warp == 0) {                           // one barrier per lane
+        if (lane < S::kStages) mbar_init(full + lane, 1);
+        else if (lane < 2 * S::kStages) mbar_init(empty + (lane - S::kStages), 1);
+        else if (lane < 2 * S::kStages + 2) mbar_init(acc_full + (lane - 2 * S::kStages), 1);
+        else if (lane < 2 * S::kStages + 4) mbar_init(acc_empty + (lane - 2 * S::kStages - 2), 4);   // one arrival per epilogue warp
+        if (lane == 0) *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -448,13 +444,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
     const int tile = blockIdx.x / n_ranks;
     const int c0 = (int)((long long)chunks * rank / n_ranks), c1 = (int)((long long)chunks * (rank + 1) / n_ranks);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, 1);
-        }
-        mbar_init(acc_full, 1);
-        *give_up = 0;
+    if (warp == 0) {                           // one barrier per lane
+        if (lane < kStages) mbar_init(full + lane, 1);
+        else if (lane < 2 * kStages) mbar_init(empty + (lane - kStages), 1);
+        else if (lane == 2 * kStages) mbar_init(acc_full, 1);
+        if (lane == 0) *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
