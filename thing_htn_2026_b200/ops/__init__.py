@@ -88,6 +88,10 @@ def lib():
         loaded.thn_set_pdl.argtypes = [c_int]
         loaded.thn_set_pdl.restype = None
         loaded.thn_set_pdl(0 if os.environ.get("THN_PDL", "1").strip().lower() in ("0", "false", "no", "off") else 1)
+        loaded.thn_set_stream_early.argtypes = [c_int]
+        loaded.thn_set_stream_early.restype = None
+        if os.environ.get("THN_STREAM_EARLY"):
+            loaded.thn_set_stream_early(int(os.environ["THN_STREAM_EARLY"]))
         loaded.thn_set_decode_cluster.argtypes = [c_int]
         loaded.thn_set_decode_cluster.restype = None
         loaded.thn_set_decode_cluster(0 if os.environ.get("THN_DECODE_CLUSTER", "1").strip() in ("0", "false", "off") else 1)
