@@ -322,7 +322,7 @@ def test_attention_prefill_tcgen05(n_q, n_kv, window):
 
 @pytest.mark.parametrize("splits", ["", "1", "3", "8", "12"])
 @pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 64, None), (32, 8, 128, None), (6, 3, 64, 70), (3, 1, 128, 24),
-                                               (16, 1, 64, None), (5, 5, 128, 200)])
+                                               (16, 1, 64, None), (5, 5, 128, 200), (16, 1, 128, None), (32, 2, 128, 90)])
 def test_attention_decode_tensor_cores(n_q, n_kv, D, window, splits):
     """One block per sequence (1), splits that meet in a thread-block cluster's shared memory
     (3, 8) and splits that meet in global memory (12: more than a cluster holds)."""
@@ -426,7 +426,8 @@ def test_qk_norm_rope_cache_same_bits_for_long_and_short_steps(n_q, n_kv, D, gai
 
 
 @pytest.mark.parametrize("gain_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("n_q,n_kv,D,window", [(8, 2, 128, None), (6, 6, 64, None), (16, 1, 128, 100), (32, 8, 128, None)])
+@pytest.mark.parametrize("n_q,n_kv,D,window", [(8, 2, 128, None), (6, 6, 64, None), (16, 1, 128, 100), (32, 8, 128, None),
+                                               (12, 2, 64, None)])
 def test_qkv_attention_fused_decode_equals_two_kernels(n_q, n_kv, D, window, gain_dtype):
     """A single-token step through the one fused kernel (q/k norm, rotation, cache write,
     attention) gives, bit for bit, the output and the cache of the two separate kernels.
