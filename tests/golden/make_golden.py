@@ -105,7 +105,9 @@ def run(reference_root, dtype):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py REFERENCE_CHECKOUT")
+    root = sys.argv[1]
     out = {"float32": run(root, torch.float32)}
     # a fresh import state is not needed: the module keeps no weights
     out["bfloat16"] = run(root, torch.bfloat16)
