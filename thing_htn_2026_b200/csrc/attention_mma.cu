@@ -872,6 +872,51 @@ THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
 THN_API void thn_set_decode_cluster(int enabled) { g_decode_cluster = enabled ? 1 : 0; }
 THN_API int thn_attention_decode_cluster_splits() { return g_decode_cluster ? kMaxClusterSplits : 0; }
 
+namespace {
+// How many clusters of c blocks of the single-token kernel (fused or not) the GPU holds at once.
+template <int D, bool FUSED>
+int decode_clusters_resident(int c) {
+    static int resident[kMaxClusterSplits + 1] = {0};
+    static bool known[kMaxClusterSplits + 1] = {false};
+    if (c < 2 || c > kMaxClusterSplits) return 0;
+    if (!known[c]) {
+        known[c] = true;
+        if (configure_decode<D, 2, FUSED, true>() != THN_OK) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 64, (unsigned)c);
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = decode_smem<D, 2>();
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 1;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = (unsigned)c;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<D, 2, FUSED, true>, &config) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        resident[c] = n;
+    }
+    return resident[c];
+}
+}  // namespace
+
+// The largest number of splits (2 .. 8) with which n_pairs (sequence, kv head) clusters of the
+// single-token kernel are all resident at once, so that the step's attention is one wave; 0 if
+// there is none (then one block per pair, or splits that meet in global memory).
+THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_pairs) {
+    if (!g_decode_cluster) return 0;
+    for (int c = kMaxClusterSplits; c >= 2; --c) {
+        const int fits = head_dim == 64 ? (fused ? decode_clusters_resident<64, true>(c) : decode_clusters_resident<64, false>(c))
+                                        : (fused ? decode_clusters_resident<128, true>(c) : decode_clusters_resident<128, false>(c));
+        if (fits >= n_pairs) return c;
+    }
+    return 0;
+}
+
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
 // counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the
 // last block of each (sequence, kv head) combines the splits itself; null: a second kernel

@@ -67,6 +67,7 @@ _SIGNATURES = {
                                   c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
+    "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
     "thn_attention_prefill_tile_rows": [],
     "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
@@ -487,15 +488,20 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int
     return out
 
 
-def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128) -> int:
+def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bool = False) -> int:
     """Splits of the key range per (sequence, kv head) so that a single-token step fills the
     GPU with one wave of blocks.  It depends on the batch only, never on the lengths, so a captured
-    step stays valid while the sequences grow."""
+    step stays valid while the sequences grow.  Up to eight splits are the blocks of one
+    thread-block cluster, and a cluster needs all its blocks resident in one part of the GPU, so
+    the count is the largest for which every cluster of the step fits at once."""
     if os.environ.get("THN_DECODE_SPLITS"):
         return int(os.environ["THN_DECODE_SPLITS"])
+    pairs = max(1, n_seqs * n_kv)
+    one_wave = lib().thn_attention_decode_one_wave_splits(head_dim, int(fused), pairs)
+    if one_wave:
+        return one_wave
     capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
-    most = lib().thn_attention_decode_cluster_splits() or 16      # a cluster holds at most 8 blocks
-    return max(1, min(most, capacity // max(1, n_seqs * n_kv)))
+    return max(1, min(16, capacity // pairs))
 
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
@@ -541,7 +547,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
     if tuple(qkv.shape) != (n_seqs, width):
         raise KernelError(f"qkv_attention: qkv is {tuple(qkv.shape)}, expected {(n_seqs, width)}")
-    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim)
+    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim, fused=True)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     scratch = torch.empty(need, dtype=torch.float32, device=qkv.device) if need else None
     counters = _counter_buffer(n_seqs * kv.n_kv, qkv.device) if n_splits > 1 else None
