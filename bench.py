@@ -194,7 +194,7 @@ def run_ours(args):
     backend.fetch(backend.launch_prefill(slots, [r.tokens for r in probe]))
     backend._set_composition(slots)
     mark = ops.launch_count
-    backend._decode_program(args.batch)
+    backend._decode_program(args.batch, ops.context_class(16)[1])
     backend.cache.commit(list(slots), [1] * args.batch)
     own_per_step = ops.launch_count - mark
     torch.cuda.synchronize()

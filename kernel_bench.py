@@ -110,6 +110,11 @@ def prefill_products(args):
     assert int(err.item()) == 0
 
 
+def results_print(results):
+    for name, entry in results.items():
+        print(name, json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in entry.items()}))
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--batch", type=int, default=8)
@@ -117,6 +122,9 @@ def main():
     parser.add_argument("--reps", type=int, default=20)
     parser.add_argument("--prefill-rows", type=int, default=0,
                         help="instead of the decode kernels, time the many-row products at this row count")
+    parser.add_argument("--only-attention", action="store_true", help="time the decode attention alone")
+    parser.add_argument("--splits", default="", help="comma-separated split counts for the decode attention "
+                        "(default: the library's own choice)")
     args = parser.parse_args()
     if args.prefill_rows:
         return prefill_products(args)
@@ -129,7 +137,7 @@ def main():
 
     shapes = {"qkv": ((NQ + 2 * NKV) * D, H), "o": (H, NQ * D), "gate_up": (2 * I, H), "down": (H, I),
               "lm_head": (V, H)}
-    for name, (n, k) in shapes.items():
+    for name, (n, k) in ({} if args.only_attention else shapes).items():
         copies = max(2, int(2 * L2_BYTES / (n * k * 2)) + 1)
         weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
         x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
@@ -170,10 +178,13 @@ def main():
     for view in views:
         view.storage.normal_()
     nbytes = m * ctx * 2 * NKV * D * 2
-    us = time_cold(lambda i: ops.attention_decode_bf16(q, rows, views[i], NQ, D ** -0.5, None, err), n_copies,
-                   args.reps)
-    results[f"attention_decode_b{m}_ctx{ctx}"] = {"bytes": nbytes, "own_us": us, "own_gbs": nbytes / us / 1e3,
-                                                  "splits": ops.decode_splits(m, NKV, dev)}
+    for splits in [int(s) for s in args.splits.split(",") if s] or [ops.decode_splits(m, NKV, dev, D, context=ctx)]:
+        us = time_cold(lambda i: ops.attention_decode_bf16(q, rows, views[i], NQ, D ** -0.5, None, err,
+                                                           n_splits=splits), n_copies, args.reps)
+        results[f"attention_decode_b{m}_ctx{ctx}_splits{splits}"] = {"bytes": nbytes, "own_us": us,
+                                                                     "own_gbs": nbytes / us / 1e3}
+    if args.only_attention:
+        return results_print(results)
 
     # the small kernels (latency-bound at this size)
     h = torch.randn(m, H, device=dev, dtype=torch.bfloat16)
@@ -185,8 +196,7 @@ def main():
     logits = torch.randn(m, V, device=dev, dtype=torch.float32)
     results["choose_tokens"] = {"own_us": time_cold(lambda i: ops.choose_tokens(logits), 1, args.reps)}
     assert int(err.item()) == 0, "a kernel reported an error"
-    for name, entry in results.items():
-        print(name, json.dumps({k: (round(v, 2) if isinstance(v, float) else v) for k, v in entry.items()}))
+    results_print(results)
 
 
 if __name__ == "__main__":

@@ -156,3 +156,20 @@ def test_random_weights_engine_runs(tiny_models):
     engine = Engine.from_config(config_from_dict(tiny.config_json("b")), seed=3, dtype="bfloat16")
     tokens, steps = collect(engine, [[1, 2, 3], [4]], 5)
     assert len(steps) == 5 and all(len(t) == 5 for t in tokens)
+
+
+def test_greedy_across_classes_of_context_length(tiny_models, monkeypatch):
+    """A captured decode step is replayed only within its class of context length.  With the
+    first class ending at 128 keys the longer sequence passes through three classes while it
+    generates, the shorter one ends earlier, and every token still is the plain argmax."""
+    from thing_htn_2026_b200 import ops
+    monkeypatch.setattr(ops, "LONG_CONTEXT", 128)
+    name = "d"
+    prompts = [tiny.tokens(name, n, 800 + i) for i, n in enumerate([100, 30])]
+    engine = engine_for(tiny_models[name], "bfloat16")
+    tokens, steps = collect(engine, prompts, [180, 40])
+    assert [len(t) for t in tokens] == [180, 40]
+    for prompt, emitted in zip(prompts, tokens):
+        check_greedy(tiny_models[name], "bfloat16", prompt, emitted)
+    assert {(2, 0), (2, 1), (1, 1), (1, 2)} <= set(engine.backend.graphs), sorted(engine.backend.graphs)
+    engine.backend.cache.check()

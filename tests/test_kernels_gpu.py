@@ -279,6 +279,9 @@ def attention_case(kernel, dtype, n_q, n_kv, D, lengths, new_counts, window, see
         got = o.attention_prefill_bf16(q, rows, fix.kv, n_q, scale, window, err)
     elif kernel == "tcgen05":
         got = o.attention_prefill_tcgen05(q, rows, fix.kv, n_q, scale, window, err)
+    elif kernel == "decode_long":
+        rows.max_context = max(lengths)           # what the engine knows on the host
+        got = o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, window, err)
     elif kernel.startswith("decode"):
         got = o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, window, err,
                                       n_splits=int(kernel[6:]) if len(kernel) > 6 else None)
@@ -320,12 +323,12 @@ def test_attention_prefill_tcgen05(n_q, n_kv, window):
     close(got, want, dtype, "tcgen05 attention, continued prompts")
 
 
-@pytest.mark.parametrize("splits", ["", "1", "3", "8", "12"])
+@pytest.mark.parametrize("splits", ["", "1", "3", "8", "12", "32"])
 @pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 64, None), (32, 8, 128, None), (6, 3, 64, 70), (3, 1, 128, 24),
                                                (16, 1, 64, None), (5, 5, 128, 200), (16, 1, 128, None), (32, 2, 128, 90)])
 def test_attention_decode_tensor_cores(n_q, n_kv, D, window, splits):
     """One block per sequence (1), splits that meet in a thread-block cluster's shared memory
-    (3, 8) and splits that meet in global memory (12: more than a cluster holds)."""
+    (3, 8) and splits that meet in global memory (12, 32: more than a cluster holds)."""
     dtype = torch.bfloat16
     lengths = [700, 64, 65, 1, 333, 128]
     got, want = attention_case("decode" + splits, dtype, n_q, n_kv, D, lengths, [1] * len(lengths), window)
@@ -361,6 +364,32 @@ def test_attention_finds_a_far_key(kernel, dtype):
     head = got[row].reshape(n_q, D)[2].float()
     assert (head - holder["v"]).abs().max() < 2e-2, "the far key did not win"
     close(got, want, dtype, "far key", scale=4)
+
+
+def test_attention_decode_long_context_finds_a_far_key():
+    """A step that is known to hold many keys divides each key range among more blocks than a
+    cluster has.  One key thousands of places back dominates a head of the long sequence; a
+    short sequence shares the step, and most of its splits are empty."""
+    o = ops()
+    dtype = torch.bfloat16
+    n_q, n_kv, D = 4, 2, 128
+    lengths = [o.LONG_CONTEXT + 150, 70]
+    target = 4321
+    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=max(lengths)) > o.lib().thn_attention_decode_cluster_splits()
+    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=o.LONG_CONTEXT - 1) == o.decode_splits(len(lengths), n_kv, DEV, D)
+    holder = {}
+
+    def peak(q_all, k_all, v_all):
+        direction = torch.zeros(D)
+        direction[9] = 1.0
+        q_all[0][-1, 3] = (direction * 40).to(dtype)        # head 3 -> kv head 1
+        k_all[0][target, 1] = (direction * 40).to(dtype)
+        holder["v"] = v_all[0][target, 1].float()
+
+    got, want = attention_case("decode_long", dtype, n_q, n_kv, D, lengths, [1, 1], None, peak=peak)
+    head = got[0].reshape(n_q, D)[3].float()
+    assert (head - holder["v"]).abs().max() < 2e-2, "the far key did not win"
+    close(got, want, dtype, "decode attention, long context", scale=4)
 
 
 @pytest.mark.parametrize("kernel,dtype", [("generic", torch.float32), ("prefill", torch.bfloat16),

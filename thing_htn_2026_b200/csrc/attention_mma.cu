@@ -428,9 +428,11 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     }
     cp_async_commit();
 
-    auto issue = [&](int t, int stage) {
+    // (the page of a tile is looked up a tile before its loads are issued: the loads' addresses
+    // wait for it, and a lookup per tile in the loop would stall the block once per tile)
+    auto page_of = [&](int t) { return t < t_end ? pages[t] : 0; };
+    auto issue = [&](int t, int stage, int page) {
         if (t < t_end) {
-            const int page = pages[t];
             if (page < 0) {
                 if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
             } else {
@@ -451,8 +453,10 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
             angle_s[e] = fused.sin_tab[(size_t)at * kHalf + lane * E + e];
         }
     }
-    issue(t_begin, 0);
-    if (kStages == 3) issue(t_begin + 1, 1);
+#pragma unroll
+    for (int ahead = 0; ahead < kStages - 1; ++ahead)                                   // kStages - 1 tiles in flight
+        issue(t_begin + ahead, ahead, page_of(t_begin + ahead));
+    int page_next = page_of(t_begin + kStages - 1);
 
     // the first tiles are on their way while the block prepares its queries
     if (FUSED) {
@@ -493,7 +497,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         }
         if (patches && warp == 0) norm_rotate_head<D>(raw_k_lo, raw_k_hi, kg_lo, kg_hi, fused.eps, c, sn, new_k_lo, new_k_hi);
     }
-    if (kStages == 3) cp_async_wait<2>(); else cp_async_wait<1>();          // Q has landed
+    cp_async_wait<kStages - 1>();                                           // Q has landed
     __syncthreads();
     uint32_t qf[D / 16][4];
 #pragma unroll
@@ -509,15 +513,11 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     st.init();
     const int tq = lane & 3;
 
-    for (int t = t_begin; t < t_end; ++t) {
-        const int stage = (t - t_begin) % kStages;
-        if (kStages == 3) {
-            issue(t + 2, (stage + 2) % 3);
-            cp_async_wait<2>();
-        } else {
-            issue(t + 1, stage ^ 1);
-            cp_async_wait<1>();
-        }
+    for (int t = t_begin, stage = 0; t < t_end; ++t, stage = stage + 1 == kStages ? 0 : stage + 1) {
+        const int page_now = page_next;
+        page_next = page_of(t + kStages);
+        issue(t + kStages - 1, stage == 0 ? kStages - 1 : stage - 1, page_now);     // into the buffer the last tile left
+        cp_async_wait<kStages - 1>();
         __syncthreads();
         if (FUSED && patches && t == t_last) {
             // the tile came from the cache without this step's token: put it in, here and there
@@ -785,40 +785,102 @@ int configure_decode() {
 constexpr int kMaxClusterSplits = 8;      // the portable cluster size; clusters of 16 measured slower than 8 (12.1 -> 14.1 us at batch 1, 4,096 keys)
 int g_decode_cluster = 1;
 
-template <int D>
+// Blocks of the single-token kernel with STAGES tile buffers that one SM holds at a time.
+template <int D, int STAGES>
 int decode_blocks_per_sm() {
-    if (configure_decode<D, 2, false, false>() != THN_OK) return 1;
-    int blocks = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attention_decode_kernel<D, 2, false, false>, kThreads,
-                                                                  decode_smem<D, 2>());
-    return (e == cudaSuccess && blocks > 0) ? blocks : 1;
+    static int blocks = 0;
+    if (blocks == 0) {
+        blocks = -1;
+        if (configure_decode<D, STAGES, false, false>() == THN_OK) {
+            int n = 0;
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, attention_decode_kernel<D, STAGES, false, false>, kThreads, decode_smem<D, STAGES>());
+            if (e == cudaSuccess && n > 0) blocks = n; else cudaGetLastError();
+        }
+    }
+    return blocks > 0 ? blocks : 1;
 }
 
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 1;
+    }
+    return sms;
+}
+
+// How many clusters of c blocks of the single-token kernel (STAGES tile buffers, fused or not) the
+// GPU holds at once.
+template <int D, int STAGES, bool FUSED>
+int decode_clusters_resident(int c) {
+    static int resident[kMaxClusterSplits + 1] = {0};
+    static bool known[kMaxClusterSplits + 1] = {false};
+    if (c < 2 || c > kMaxClusterSplits) return 0;
+    if (!known[c]) {
+        known[c] = true;
+        if (configure_decode<D, STAGES, FUSED, true>() != THN_OK) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 64, (unsigned)c);
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = decode_smem<D, STAGES>();
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 1;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = (unsigned)c;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<D, STAGES, FUSED, true>, &config) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        resident[c] = n;
+    }
+    return resident[c];
+}
+
+template <int D, int STAGES, bool FUSED, bool CLUSTER>
+int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
+                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                       cudaStream_t stream, const FusedInput& fused) {
+    int configured = configure_decode<D, STAGES, FUSED, CLUSTER>();
+    if (configured != THN_OK) return configured;
+    dim3 grid(n_seqs, kv.n_kv, n_splits);
+    if (CLUSTER)      // the splits of a (sequence, kv head) as one cluster along z
+        thn_launch_cluster(attention_decode_kernel<D, STAGES, FUSED, CLUSTER>, grid, kThreads, decode_smem<D, STAGES>(),
+                           stream, dim3(1, 1, n_splits), (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,
+                           row_slot, row_pos, kv, n_q, n_splits, scale * kLog2e, window, counters, err, fused);
+    else
+        thn_launch(attention_decode_kernel<D, STAGES, FUSED, CLUSTER>, grid, kThreads, decode_smem<D, STAGES>(), stream,
+                   (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
+                   scale * kLog2e, window, counters, err, fused);
+    return thn_launch_status(CLUSTER ? "attention_decode (cluster)" : "attention_decode");
+}
+
+// A block keeps STAGES - 1 tiles on their way while it works on one.  A block that has an SM to
+// itself needs about five in flight for its share of the memory bandwidth; with more blocks on an
+// SM each has less shared memory and needs less.  The deepest pipeline with which the whole grid
+// is still resident at once is taken: it depends on the batch only, not on the lengths.
 template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
                   cudaStream_t stream, FusedInput fused = FusedInput{}) {
-    dim3 grid(n_seqs, kv.n_kv, n_splits);
+#define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
+    const int n_pairs = n_seqs * kv.n_kv;
     if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster) {
-        // the splits of a (sequence, kv head) as one cluster along z
-        int configured = configure_decode<D, 2, FUSED, true>();
-        if (configured != THN_OK) return configured;
-        thn_launch_cluster(attention_decode_kernel<D, 2, FUSED, true>, grid, kThreads, decode_smem<D, 2>(), stream,
-                           dim3(1, 1, n_splits), (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot,
-                           row_pos, kv, n_q, n_splits, scale * kLog2e, window, counters, err, fused);
-        return thn_launch_status("attention_decode (cluster)");
+        if (decode_clusters_resident<D, 6, FUSED>(n_splits) >= n_pairs) return launch_decode_with<D, 6, FUSED, true>(THN_DECODE_ARGS);
+        if (decode_clusters_resident<D, 3, FUSED>(n_splits) >= n_pairs) return launch_decode_with<D, 3, FUSED, true>(THN_DECODE_ARGS);
+        return launch_decode_with<D, 2, FUSED, true>(THN_DECODE_ARGS);
     }
-    int configured = n_splits == 1 ? configure_decode<D, 3, FUSED, false>() : configure_decode<D, 2, FUSED, false>();
-    if (configured != THN_OK) return configured;
-    if (n_splits == 1)
-        thn_launch(attention_decode_kernel<D, 3, FUSED, false>, grid, kThreads, decode_smem<D, 3>(), stream,
-                   (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
-                   scale * kLog2e, window, counters, err, fused);
-    else
-        thn_launch(attention_decode_kernel<D, 2, FUSED, false>, grid, kThreads, decode_smem<D, 2>(), stream,
-                   (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, row_slot, row_pos, kv, n_q, n_splits,
-                   scale * kLog2e, window, counters, err, fused);
-    int status = thn_launch_status("attention_decode");
+    const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
+    int status;
+    if (n_blocks <= sms * decode_blocks_per_sm<D, 6>()) status = launch_decode_with<D, 6, FUSED, false>(THN_DECODE_ARGS);
+    else if (n_blocks <= sms * decode_blocks_per_sm<D, 3>() || n_splits == 1) status = launch_decode_with<D, 3, FUSED, false>(THN_DECODE_ARGS);
+    else status = launch_decode_with<D, 2, FUSED, false>(THN_DECODE_ARGS);
+#undef THN_DECODE_ARGS
     if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
     thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
                                                                             n_splits, D);
@@ -864,7 +926,7 @@ THN_API long long thn_attention_decode_scratch_floats(int n_seqs, int n_q, int n
 // Blocks of the decode kernel that one SM holds at a time (for choosing n_splits so that
 // the grid is one wave).
 THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
-    return head_dim == 64 ? decode_blocks_per_sm<64>() : decode_blocks_per_sm<128>();
+    return head_dim == 64 ? decode_blocks_per_sm<64, 2>() : decode_blocks_per_sm<128, 2>();
 }
 
 // 0: the splits of a sequence always meet in global memory; 1 (default): in a thread-block
@@ -872,46 +934,14 @@ THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
 THN_API void thn_set_decode_cluster(int enabled) { g_decode_cluster = enabled ? 1 : 0; }
 THN_API int thn_attention_decode_cluster_splits() { return g_decode_cluster ? kMaxClusterSplits : 0; }
 
-namespace {
-// How many clusters of c blocks of the single-token kernel (fused or not) the GPU holds at once.
-template <int D, bool FUSED>
-int decode_clusters_resident(int c) {
-    static int resident[kMaxClusterSplits + 1] = {0};
-    static bool known[kMaxClusterSplits + 1] = {false};
-    if (c < 2 || c > kMaxClusterSplits) return 0;
-    if (!known[c]) {
-        known[c] = true;
-        if (configure_decode<D, 2, FUSED, true>() != THN_OK) return 0;
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(1, 64, (unsigned)c);
-        config.blockDim = dim3(kThreads);
-        config.dynamicSmemBytes = decode_smem<D, 2>();
-        cudaLaunchAttribute attribute[1];
-        attribute[0].id = cudaLaunchAttributeClusterDimension;
-        attribute[0].val.clusterDim.x = 1;
-        attribute[0].val.clusterDim.y = 1;
-        attribute[0].val.clusterDim.z = (unsigned)c;
-        config.attrs = attribute;
-        config.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<D, 2, FUSED, true>, &config) != cudaSuccess) {
-            cudaGetLastError();
-            n = 0;
-        }
-        resident[c] = n;
-    }
-    return resident[c];
-}
-}  // namespace
-
 // The largest number of splits (2 .. 8) with which n_pairs (sequence, kv head) clusters of the
 // single-token kernel are all resident at once, so that the step's attention is one wave; 0 if
 // there is none (then one block per pair, or splits that meet in global memory).
 THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_pairs) {
     if (!g_decode_cluster) return 0;
     for (int c = kMaxClusterSplits; c >= 2; --c) {
-        const int fits = head_dim == 64 ? (fused ? decode_clusters_resident<64, true>(c) : decode_clusters_resident<64, false>(c))
-                                        : (fused ? decode_clusters_resident<128, true>(c) : decode_clusters_resident<128, false>(c));
+        const int fits = head_dim == 64 ? (fused ? decode_clusters_resident<64, 2, true>(c) : decode_clusters_resident<64, 2, false>(c))
+                                        : (fused ? decode_clusters_resident<128, 2, true>(c) : decode_clusters_resident<128, 2, false>(c));
         if (fits >= n_pairs) return c;
     }
     return 0;

@@ -1,5 +1,5 @@
 """Device side of the generation loop: prefill through the step function, single-token
-steps as one CUDA graph per batch size, token choice on the device, tokens back to the
+steps as one CUDA graph per batch size and class of context length, token choice on the device, tokens back to the
 host through a ring of pinned buffers.
 
 Per-sequence state of fixed size, indexed by slot (beside ``seq_lens``): the token the
@@ -57,7 +57,7 @@ class DeviceBackend:
         self.out_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
         self.row_slot = torch.zeros(n, dtype=torch.int32, device=dev)
         self.row_pos = torch.zeros(n, dtype=torch.int32, device=dev)
-        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}     # (batch, context class)
         self._composition: Optional[Tuple[int, ...]] = None
         self._ring = [(torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
                       for _ in range(ring)]
@@ -122,14 +122,15 @@ class DeviceBackend:
         self._choose(logits, slots_dev, out)
         return self._send(out, len(slots))
 
-    def _decode_program(self, batch: int) -> None:
+    def _decode_program(self, batch: int, max_context: int) -> None:
         """One token for each of the first ``batch`` slots of ``slots_buf``; everything it
-        reads and writes is per-sequence state or a static buffer."""
+        reads and writes is per-sequence state or a static buffer.  ``max_context`` bounds
+        the keys a sequence holds after the step, for as long as the program is replayed."""
         slots = self.slots_buf[:batch]
         cu = self.cu_buf[:batch + 1]
         tokens = ops.gather_i32(self.last_token, slots, out=self.tokens_in[:batch])
         rows = ops.step_rows(cu, slots, self.cache.seq_lens, batch, 1,
-                             out=(self.row_slot[:batch], self.row_pos[:batch]))
+                             out=(self.row_slot[:batch], self.row_pos[:batch]), max_context=max_context)
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
         h, d = self.model.hidden(tokens, ctx)
         logits = self.model.logits(h, d, None, self.err)
@@ -145,7 +146,7 @@ class DeviceBackend:
         self.slots_buf[:len(slots)].copy_(stage[:len(slots)], non_blocking=True)
         self._composition = key
 
-    def _capture(self, batch: int) -> None:
+    def _capture(self, batch: int, context_class: int, max_context: int) -> None:
         """Warm the program up on the scratch slot (it advances nothing that lives), then
         record it."""
         scratch = torch.full((batch,), self._scratch_slot, dtype=torch.int32, device=self.device)
@@ -156,25 +157,27 @@ class DeviceBackend:
         with torch.cuda.stream(side):
             for _ in range(2):
                 self.cache.seq_lens[self._scratch_slot] = 0
-                self._decode_program(batch)
+                self._decode_program(batch, max_context)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self._decode_program(batch)
+            self._decode_program(batch, max_context)
         self.cache.seq_lens[self._scratch_slot] = 0
         torch.cuda.synchronize()
-        self.graphs[batch] = graph
+        self.graphs[(batch, context_class)] = graph
 
     def launch_decode(self, slots: Sequence[int]) -> _Handle:
         batch = len(slots)
-        if self.use_graphs and batch not in self.graphs:
-            self._capture(batch)
+        longest = max(self.cache.length(slot) for slot in slots) + 1
+        context_class, max_context = ops.context_class(longest)
+        if self.use_graphs and (batch, context_class) not in self.graphs:
+            self._capture(batch, context_class, max_context)
         self._set_composition(slots)
         if self.use_graphs:
-            self.graphs[batch].replay()
+            self.graphs[(batch, context_class)].replay()
         else:
-            self._decode_program(batch)
+            self._decode_program(batch, max_context)
         self.cache.commit(list(slots), [1] * batch)
         return self._send(self.out_tokens, batch)
 

@@ -106,7 +106,8 @@ class StepRunner:
             at += len(part)
         tokens, cu_dev, slots_dev, want_dev, tile_row0_dev, tile_rows_dev = views
 
-        rows = ops.step_rows(cu_dev, slots_dev, self.cache.seq_lens, n_rows, max(counts))
+        longest = max(self.cache.length(slot) + c for slot, c in zip(slots, counts))
+        rows = ops.step_rows(cu_dev, slots_dev, self.cache.seq_lens, n_rows, max(counts), max_context=longest)
         if tile_row0:
             rows.tile_row0, rows.tile_rows, rows.n_tiles = tile_row0_dev, tile_rows_dev, len(tile_row0)
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err)

@@ -174,10 +174,26 @@ class StepRows:
     tile_row0: Optional[torch.Tensor] = None
     tile_rows: Optional[torch.Tensor] = None
     n_tiles: int = 0
+    # Host knowledge: the most keys a row of this step may see (an upper bound; None: unknown).
+    # Kernels may divide their work by it, which changes a result by rounding at most.  A step
+    # captured as a graph is replayed only while its bound holds (see context_class).
+    max_context: Optional[int] = None
+
+
+LONG_CONTEXT = 8192     # keys; a single-token step of few long sequences divides each key range further
+
+
+def context_class(longest: int) -> Tuple[int, int]:
+    """(class, bound) of a step whose longest sequence holds ``longest`` keys: class 0 below
+    LONG_CONTEXT, then one class per doubling.  Steps of one class make the same choices, so
+    one captured graph serves them; ``bound`` is the class's ``max_context``."""
+    k = (max(0, int(longest)) // LONG_CONTEXT).bit_length()
+    return k, (LONG_CONTEXT << k) - 1
 
 
 def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Tensor, n_rows: int,
-              max_q_len: int, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> StepRows:
+              max_q_len: int, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+              max_context: Optional[int] = None) -> StepRows:
     _need(cu_seqlens, "step_rows cu_seqlens", torch.int32)
     _need(slots, "step_rows slots", torch.int32)
     _need(seq_lens, "step_rows seq_lens", torch.int32)
@@ -189,7 +205,7 @@ def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Ten
         row_slot, row_pos = out
     _call("thn_step_rows", _ptr(row_slot), _ptr(row_pos), _ptr(cu_seqlens), _ptr(slots), _ptr(seq_lens), n_seqs,
           _stream())
-    return StepRows(row_slot, row_pos, slots, cu_seqlens, n_rows, n_seqs, max_q_len)
+    return StepRows(row_slot, row_pos, slots, cu_seqlens, n_rows, n_seqs, max_q_len, max_context=max_context)
 
 
 def advance(seq_lens: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor) -> None:
@@ -488,16 +504,29 @@ def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int
     return out
 
 
-def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bool = False) -> int:
+DECODE_MAX_SPLITS = 32     # the splits of a key range are combined by the lanes of one warp
+
+
+def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bool = False,
+                  context: Optional[int] = None) -> int:
     """Splits of the key range per (sequence, kv head) so that a single-token step fills the
-    GPU with one wave of blocks.  It depends on the batch only, never on the lengths, so a captured
-    step stays valid while the sequences grow.  Up to eight splits are the blocks of one
-    thread-block cluster, and a cluster needs all its blocks resident in one part of the GPU, so
-    the count is the largest for which every cluster of the step fits at once."""
+    GPU with one wave of blocks.  It depends on the batch and on ``context`` (the step's
+    ``max_context``, a bound that holds for every replay of a captured step), never on the
+    lengths themselves.  Up to eight splits are the blocks of one thread-block cluster, and a
+    cluster needs all its blocks resident in one part of the GPU, so the count is the largest
+    for which every cluster of the step fits at once."""
     if os.environ.get("THN_DECODE_SPLITS"):
         return int(os.environ["THN_DECODE_SPLITS"])
     pairs = max(1, n_seqs * n_kv)
     one_wave = lib().thn_attention_decode_one_wave_splits(head_dim, int(fused), pairs)
+    if context is not None and context >= LONG_CONTEXT:
+        # Few long sequences: a block works through its tiles one after the other, and a cluster's
+        # blocks are too few to draw the memory bandwidth.  Two blocks per SM, meeting in global
+        # memory, read 32,768 keys of one sequence in 33 us against 56 us (B200, 8 kv heads);
+        # below 8,192 keys the cluster's cheaper merge wins.
+        wide = min(DECODE_MAX_SPLITS, 2 * _sm_count_of(device) // pairs)
+        if wide >= 2 * max(1, one_wave):
+            return wide
     if one_wave:
         return one_wave
     capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
@@ -512,7 +541,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _need(q, "attention q", torch.bfloat16)
     n_seqs = rows.n_rows
     if n_splits is None:
-        n_splits = decode_splits(n_seqs, kv.n_kv, q.device, kv.head_dim)
+        n_splits = decode_splits(n_seqs, kv.n_kv, q.device, kv.head_dim, context=rows.max_context)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     if need and scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
@@ -547,7 +576,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
     if tuple(qkv.shape) != (n_seqs, width):
         raise KernelError(f"qkv_attention: qkv is {tuple(qkv.shape)}, expected {(n_seqs, width)}")
-    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim, fused=True)
+    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim, fused=True, context=rows.max_context)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     scratch = torch.empty(need, dtype=torch.float32, device=qkv.device) if need else None
     counters = _counter_buffer(n_seqs * kv.n_kv, qkv.device) if n_splits > 1 else None
