@@ -38,6 +38,8 @@ def test_bench_line_has_the_contract_keys():
     assert line["roofline"]["bound"] == "hbm" and line["roofline"]["unit"] == "GB/s"
     assert abs(line["roofline"]["frac"] - line["roofline"]["achieved"] / line["roofline"]["peak"]) < 1e-9
     assert set(line["points"]) == {"decode_b1", "decode_b64"}
+    assert set(line["workloads"]) == {"gen_1x512x32", "gen_4x2048x32", "gen_16x512x128"}
+    assert all(v > 0 for v in line["workloads"].values())
     assert set(line["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
     assert line["gpu_launches"] > 0
 
