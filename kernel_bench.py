@@ -2,7 +2,7 @@
 operands (the weights rotate through more copies than the L2 cache holds), with CUDA
 events, and prints achieved GB/s beside the vendor library's product on the same shape.
 
-    python kernel_bench.py [--batch 8] [--context 640] [--reps 20]
+    python kernel_bench.py [--batch 8] [--context 640] [--reps 20] [--sizes 4b|8b|14b]
 """
 
 from __future__ import annotations
@@ -16,7 +16,9 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import torch  # noqa: E402
 
-H, I, V, NQ, NKV, D = 2560, 9728, 151936, 32, 8, 128
+SIZES = {"4b": (2560, 9728, 151936, 32, 8, 128), "8b": (4096, 12288, 151936, 32, 8, 128),
+         "14b": (5120, 17408, 151936, 40, 8, 128)}          # hidden, intermediate, vocab, q heads, kv heads, head size
+H, I, V, NQ, NKV, D = SIZES["4b"]
 L2_BYTES = 126 * 2 ** 20
 
 
@@ -125,7 +127,10 @@ def main():
     parser.add_argument("--only-attention", action="store_true", help="time the decode attention alone")
     parser.add_argument("--splits", default="", help="comma-separated split counts for the decode attention "
                         "(default: the library's own choice)")
+    parser.add_argument("--sizes", default="4b", choices=sorted(SIZES), help="layer sizes of Qwen3-4B, -8B or -14B")
     args = parser.parse_args()
+    global H, I, V, NQ, NKV, D
+    H, I, V, NQ, NKV, D = SIZES[args.sizes]
     if args.prefill_rows:
         return prefill_products(args)
     from thing_htn_2026_b200 import ops

@@ -290,13 +290,18 @@ def _sm_count_of(device) -> int:
     return _sm_count[index]
 
 
-# Products with at most this many rows go to this library's weight-streaming kernel when the
-# reduction is at least STREAM_MIN_K deep or the weight has at least STREAM_MIN_N rows;
-# measured on B200 at 8 rows (kernel_bench.py): it beats the vendor library at K = 4096 and
-# 9728 and on the head (9.3 vs 10.3 us, 14.1 vs 20.4 us, 119 vs 127 us) and loses at K = 2560
-# (10.4 vs 7.5 us, 20.0 vs 17.5 us) and beyond 16 rows.
+# Products with at most STREAM_MAX_ROWS rows go to this library's weight-streaming kernel where it
+# beats the vendor library (kernel_bench.py on B200, 1 to 16 rows, at the layer sizes of Qwen3-4B,
+# -8B and -14B): a weight of at most STREAM_MAX_N rows (so few 128-row tiles that a cluster of
+# four or more blocks shares each) under a reduction at least STREAM_MIN_K deep: o and down at
+# 2560 x 4096, 2560 x 9728, 4096 x 4096, 4096 x 12288 (7.1 vs 10.3, 12.0 vs 20.4, 9.2 vs 12.2,
+# 19.7 vs 31.3 us at 8 rows); and a weight of at least STREAM_MIN_N rows (the head: 123 vs 127,
+# 191 vs 205, 233 vs 255 us).  The library wins on q/k/v and gate-up at every size (7.5 vs 10.0,
+# 17.5 vs 21.0, 10.9 vs 13.2, 34.4 vs 36.8, 13.8 vs 16.7, 58.0 vs 59.5 us), at 5120 x 5120 and
+# 5120 x 17408 (11.5 vs 12.5, 31.2 vs 32.7 us), and beyond 16 rows.
 STREAM_MAX_ROWS = 16
 STREAM_MIN_K = int(os.environ.get("THN_STREAM_MIN_K", 4096))
+STREAM_MAX_N = int(os.environ.get("THN_STREAM_MAX_N", 4096))
 STREAM_MIN_N = 65536
 STREAM_POLICY = os.environ.get("THN_LINEAR_STREAM", "auto")     # auto | all | none (measurement)
 
@@ -369,7 +374,7 @@ def _stream_takes(m: int, n: int, k: int, fused: bool = False) -> bool:
         return False
     if STREAM_POLICY == "all":
         return True
-    return not fused and m <= STREAM_MAX_ROWS and (k >= STREAM_MIN_K or n >= STREAM_MIN_N)
+    return not fused and m <= STREAM_MAX_ROWS and ((k >= STREAM_MIN_K and n <= STREAM_MAX_N) or n >= STREAM_MIN_N)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, err: Optional[torch.Tensor] = None) -> torch.Tensor:
