@@ -137,7 +137,7 @@ def run_ours(args):
     peak = peaks()
     torch.manual_seed(0)
     biggest = max(args.batch, 64 if not args.no_points else args.batch)
-    per_seq = PROMPT + max(args.steps + args.warmup, 64) + 64
+    per_seq = args.prompt_len + max(args.steps + args.warmup, 64) + 64
     max_tokens = max(biggest * -(-per_seq // 64) * 64, 4096)
     if not args.no_points:
         max_tokens = max(max_tokens, max(b * -(-(p + n) // 64) * 64 for b, p, n in WORKLOADS))
@@ -150,7 +150,7 @@ def run_ours(args):
 
     def decode_device(batch, steps, warmup, sample_clocks=False):
         """K graph replays timed with CUDA events; returns ms per step and context seen."""
-        requests = [Request(p, warmup + steps + 1, 0.0, 0, i) for i, p in enumerate(prompts(batch, PROMPT))]
+        requests = [Request(p, warmup + steps + 1, 0.0, 0, i) for i, p in enumerate(prompts(batch, args.prompt_len))]
         slots = backend.open_batch(requests)
         try:
             backend.fetch(backend.launch_prefill(slots, [r.tokens for r in requests]))
@@ -178,7 +178,7 @@ def run_ours(args):
                 torch.cuda.profiler.stop()
             clocks = sampler.stop() if sampler else None
             ms = start.elapsed_time(end) / steps
-            ctx_mean = PROMPT + warmup + (steps - 1) / 2.0
+            ctx_mean = args.prompt_len + warmup + (steps - 1) / 2.0
             return ms, ctx_mean, clocks, ops.launch_count - before
         finally:
             backend.close_batch(slots)
@@ -206,7 +206,7 @@ def run_ours(args):
     backend.close_batch(slots)
 
     # end to end through the public entry point
-    e2e_prompts = prompts(args.batch, PROMPT)
+    e2e_prompts = prompts(args.batch, args.prompt_len)
     n_new = args.steps + 1
     list(engine.generate(e2e_prompts, 4))                   # warm: graphs for this batch exist already
     torch.cuda.synchronize()
@@ -283,7 +283,7 @@ def run_ours(args):
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": True,
-            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+            "global_batch": args.batch, "seq_len": max(CONTEXT, args.prompt_len + args.steps + max(args.warmup, 3) + 1), "prompt_len": args.prompt_len,
             "context_mean": ctx_mean, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (a step reads all weights)", "graphs": backend.use_graphs,
             "peaks": peak["source"],
@@ -322,6 +322,7 @@ def main():
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the decode steps")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")

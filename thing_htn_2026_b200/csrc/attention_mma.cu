@@ -11,6 +11,8 @@
 // Instantiated for head sizes 64 and 128; other sizes use the generic kernel.
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -934,12 +936,21 @@ THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
 THN_API void thn_set_decode_cluster(int enabled) { g_decode_cluster = enabled ? 1 : 0; }
 THN_API int thn_attention_decode_cluster_splits() { return g_decode_cluster ? kMaxClusterSplits : 0; }
 
-// The largest number of splits (2 .. 8) with which n_pairs (sequence, kv head) clusters of the
-// single-token kernel are all resident at once, so that the step's attention is one wave; 0 if
-// there is none (then one block per pair, or splits that meet in global memory).
+// Splits (2 .. 8, the blocks of one cluster) per (sequence, kv head) for a single-token step of
+// n_pairs such pairs; 0: one block per pair.  As many as fill the SMs once with every cluster of
+// the step resident (a cluster that has to wait for the first ones to end costs a whole second
+// pass: 2.49 against 2.31 ms per step with 7 instead of 6 at batch 8), but clusters of more than
+// six blocks only where they are so few that each block has an SM to itself.  Measured inside the
+// decode step of the Qwen3-4B sizes on B200 (ms per step, 512-640 keys): batch 2: 2.245 / 2.187 /
+// 2.205 with 4 / 6 / 8; batch 4: 2.236 / 2.227 / 2.240; batch 8: 2.327 / 2.294 / 2.306 with 4 / 5
+// / 6; batch 16: 2.492 / 2.466 / 2.461 with 1 / 2 / 3.  (Timed alone, back to back, fewer and
+// larger blocks look better than they are in the step: there the next launch overlaps them.)
 THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_pairs) {
-    if (!g_decode_cluster) return 0;
-    for (int c = kMaxClusterSplits; c >= 2; --c) {
+    if (!g_decode_cluster || n_pairs <= 0) return 0;
+    const int sms = sm_count();
+    const int per_sm = head_dim == 64 ? decode_blocks_per_sm<64, 2>() : decode_blocks_per_sm<128, 2>();
+    const int most = n_pairs * kMaxClusterSplits * 2 <= sms ? kMaxClusterSplits : 6;
+    for (int c = std::min(most, per_sm * sms / n_pairs); c >= 2; --c) {
         const int fits = head_dim == 64 ? (fused ? decode_clusters_resident<64, 2, true>(c) : decode_clusters_resident<64, 2, false>(c))
                                         : (fused ? decode_clusters_resident<128, 2, true>(c) : decode_clusters_resident<128, 2, false>(c));
         if (fits >= n_pairs) return c;

@@ -514,12 +514,11 @@ DECODE_MAX_SPLITS = 32     # the splits of a key range are combined by the lanes
 
 def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bool = False,
                   context: Optional[int] = None) -> int:
-    """Splits of the key range per (sequence, kv head) so that a single-token step fills the
-    GPU with one wave of blocks.  It depends on the batch and on ``context`` (the step's
-    ``max_context``, a bound that holds for every replay of a captured step), never on the
-    lengths themselves.  Up to eight splits are the blocks of one thread-block cluster, and a
-    cluster needs all its blocks resident in one part of the GPU, so the count is the largest
-    for which every cluster of the step fits at once."""
+    """Splits of the key range per (sequence, kv head) of a single-token step: as many as fill
+    the SMs once, the splits of a pair being the blocks of one thread-block cluster (at most
+    eight, six unless the pairs are very few), all clusters resident at once.  It depends on the
+    batch and on ``context`` (the step's ``max_context``, a bound that holds for every replay of
+    a captured step), never on the lengths themselves."""
     if os.environ.get("THN_DECODE_SPLITS"):
         return int(os.environ["THN_DECODE_SPLITS"])
     pairs = max(1, n_seqs * n_kv)
@@ -532,10 +531,7 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bo
         wide = min(DECODE_MAX_SPLITS, 2 * _sm_count_of(device) // pairs)
         if wide >= 2 * max(1, one_wave):
             return wide
-    if one_wave:
-        return one_wave
-    capacity = _sm_count_of(device) * lib().thn_attention_decode_blocks_per_sm(head_dim)
-    return max(1, min(16, capacity // pairs))
+    return max(1, one_wave)
 
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
