@@ -879,9 +879,14 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     }
     const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
     int status;
+    // (One block per pair and more blocks than the GPU holds even with two buffers each: the step
+    // takes a second pass anyway, and three buffers were faster then, 3.47 against 3.73 ms per step
+    // at batch 64; with 40 and 48 sequences, one pass with two buffers, 3.00 and 3.13 against 3.23
+    // and 3.41 ms.)
     if (n_blocks <= sms * decode_blocks_per_sm<D, 6>()) status = launch_decode_with<D, 6, FUSED, false>(THN_DECODE_ARGS);
-    else if (n_blocks <= sms * decode_blocks_per_sm<D, 3>() || n_splits == 1) status = launch_decode_with<D, 3, FUSED, false>(THN_DECODE_ARGS);
-    else status = launch_decode_with<D, 2, FUSED, false>(THN_DECODE_ARGS);
+    else if (n_blocks <= sms * decode_blocks_per_sm<D, 3>()) status = launch_decode_with<D, 3, FUSED, false>(THN_DECODE_ARGS);
+    else if (n_blocks <= sms * decode_blocks_per_sm<D, 2>() || n_splits > 1) status = launch_decode_with<D, 2, FUSED, false>(THN_DECODE_ARGS);
+    else status = launch_decode_with<D, 3, FUSED, false>(THN_DECODE_ARGS);
 #undef THN_DECODE_ARGS
     if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
     thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
