@@ -75,7 +75,7 @@ def test_unequal_batches_with_slot_reuse(tiny_models, tmp_path, name, dtype):
 @pytest.mark.parametrize("name", NAMES)
 def test_single_token_steps_through_the_streaming_product(tiny_models, tmp_path, name, policy, monkeypatch):
     """At the tiny sizes the few-row products would all go to the vendor library.  Here every
-    product of a step of at most 16 rows is sent to this library's weight-streaming kernel
+    product of a step of few rows (at most `ops.STREAM_MAX_ROWS`) is sent to this library's weight-streaming kernel
     (``all``: the gate-up product fused with SwiGLU as well), the head with float32 output
     included, and the logits are held to the same measure."""
     from thing_htn_2026_b200 import ops

@@ -297,9 +297,12 @@ def _sm_count_of(device) -> int:
 # 2560 x 4096, 2560 x 9728, 4096 x 4096, 4096 x 12288 (7.1 vs 10.3, 12.0 vs 20.4, 9.2 vs 12.2,
 # 19.7 vs 31.3 us at 8 rows); and a weight of at least STREAM_MIN_N rows (the head: 123 vs 127,
 # 191 vs 205, 233 vs 255 us).  The library wins on q/k/v and gate-up at every size (7.5 vs 10.0,
-# 17.5 vs 21.0, 10.9 vs 13.2, 34.4 vs 36.8, 13.8 vs 16.7, 58.0 vs 59.5 us), at 5120 x 5120 and
-# 5120 x 17408 (11.5 vs 12.5, 31.2 vs 32.7 us), and beyond 16 rows.
-STREAM_MAX_ROWS = 16
+# 17.5 vs 21.0, 10.9 vs 13.2, 34.4 vs 36.8, 13.8 vs 16.7, 58.0 vs 59.5 us) and at 5120 x 5120 and
+# 5120 x 17408 (11.5 vs 12.5, 31.2 vs 32.7 us).  The row limit comes from whole decode steps of
+# the Qwen3-4B sizes, where a product also gains from starting under its predecessor's tail: with
+# the streaming product a step of 17 / 24 / 32 / 33 / 48 / 64 rows takes 2.49 / 2.61 / 2.74 / 2.78 /
+# 3.09 / 3.49 ms, with the library's 2.63 / 2.74 / 2.85 / 2.85 / 3.13 / 3.47 ms.
+STREAM_MAX_ROWS = 48
 STREAM_MIN_K = int(os.environ.get("THN_STREAM_MIN_K", 4096))
 STREAM_MAX_N = int(os.environ.get("THN_STREAM_MAX_N", 4096))
 STREAM_MIN_N = 65536
