@@ -1,0 +1,26 @@
+"""Host-side hints of a step: the class of context length that decides which captured decode
+graph may be replayed, and its bound on the keys a row may see."""
+
+from thing_htn_2026_b200 import ops
+
+
+def test_context_class_bounds_every_length_of_its_class():
+    first = ops.LONG_CONTEXT
+    assert ops.context_class(0) == (0, first - 1)
+    assert ops.context_class(first - 1) == (0, first - 1)
+    assert ops.context_class(first) == (1, 2 * first - 1)
+    assert ops.context_class(2 * first - 1) == (1, 2 * first - 1)
+    assert ops.context_class(2 * first) == (2, 4 * first - 1)
+    last = (-1, -1)
+    for longest in list(range(0, 5 * first, 97)) + [10 ** 6]:
+        k, bound = ops.context_class(longest)
+        assert bound >= longest, "a step's bound must hold for the step itself"
+        assert (k, bound) >= last, "classes follow the length"
+        if k:
+            assert bound < 2 * longest + 1, "a class spans one doubling"
+        last = (k, bound)
+
+
+def test_few_classes_over_a_long_generation():
+    seen = {ops.context_class(n)[0] for n in range(1, 200_000, 13)}
+    assert len(seen) <= 6, "one captured graph per class and batch size: the classes stay few"
