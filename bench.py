@@ -33,6 +33,13 @@ QWEN3_4B = dict(
     rms_norm_eps=1e-6, rope_theta=5000000.0, tie_word_embeddings=True, max_position_embeddings=4096,
     hidden_act="silu", attention_bias=False, rope_scaling=None,
 )
+# Other layer sizes of the family, for measurements beside the default run (--sizes).
+OTHER_SIZES = {
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+               num_key_value_heads=8, rope_theta=1000000.0, tie_word_embeddings=False),
+    "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
+                num_key_value_heads=8, rope_theta=1000000.0, tie_word_embeddings=False),
+}
 CONTEXT = 4096
 PROMPT = 512
 PREFILL_TOKENS = 2048
@@ -129,6 +136,8 @@ def run_ours(args):
     from thing_htn_2026_b200.engine.step import StepEntry
 
     cfg = dict(QWEN3_4B)
+    if args.sizes != "4b":
+        cfg.update(OTHER_SIZES[args.sizes])
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -273,16 +282,16 @@ def run_ours(args):
             workloads[f"gen_{batch}x{prompt_len}x{n_out}"] = batch * n_out / best
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-4B layer sizes, random bf16 weights, 1 B200)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.sizes.upper()} layer sizes, random bf16 weights, 1 B200)",
         "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-4B layer sizes", "layers": n_layers, "layers_full": full_layers,
+            "model": f"Qwen3-{args.sizes.upper()} layer sizes", "layers": n_layers, "layers_full": full_layers,
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": True,
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": bool(cfg["tie_word_embeddings"]),
             "global_batch": args.batch, "seq_len": max(CONTEXT, args.prompt_len + args.steps + max(args.warmup, 3) + 1), "prompt_len": args.prompt_len,
             "context_mean": ctx_mean, "parallelism": "single GPU",
             "l2": "inputs larger than L2 (a step reads all weights)", "graphs": backend.use_graphs,
@@ -322,6 +331,8 @@ def main():
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--sizes", default="4b", choices=["4b"] + sorted(OTHER_SIZES),
+                        help="layer sizes of Qwen3-4B (the default run), -8B or -14B")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the decode steps")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
