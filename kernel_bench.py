@@ -125,6 +125,8 @@ def main():
     parser.add_argument("--prefill-rows", type=int, default=0,
                         help="instead of the decode kernels, time the many-row products at this row count")
     parser.add_argument("--only-attention", action="store_true", help="time the decode attention alone")
+    parser.add_argument("--only-product", default="", help="time one few-row product alone: qkv, o, gate_up, down "
+                        "or lm_head")
     parser.add_argument("--splits", default="", help="comma-separated split counts for the decode attention "
                         "(default: the library's own choice)")
     parser.add_argument("--sizes", default="4b", choices=sorted(SIZES), help="layer sizes of Qwen3-4B, -8B or -14B")
@@ -142,6 +144,8 @@ def main():
 
     shapes = {"qkv": ((NQ + 2 * NKV) * D, H), "o": (H, NQ * D), "gate_up": (2 * I, H), "down": (H, I),
               "lm_head": (V, H)}
+    if args.only_product:
+        shapes = {args.only_product: shapes[args.only_product]}
     for name, (n, k) in ({} if args.only_attention else shapes).items():
         copies = max(2, int(2 * L2_BYTES / (n * k * 2)) + 1)
         weights = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
@@ -160,6 +164,9 @@ def main():
                 lambda i: ops.swiglu(torch.nn.functional.linear(x, weights[i])), copies, args.reps)
         results[f"gemm_{name}_m{m}"] = entry
         del weights
+
+    if args.only_product:
+        return results_print(results)
 
     # decode attention over `context` cached tokens per sequence
     ctx = args.context
