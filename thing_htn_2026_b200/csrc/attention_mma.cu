@@ -413,9 +413,10 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
     const int t_first = first_key / kTile, t_last = pos / kTile;
     const int n_tiles = t_last - t_first + 1;
-    const int per_split = (n_tiles + n_splits - 1) / n_splits;
-    const int t_begin = t_first + split * per_split;
-    const int t_end = min(t_begin + per_split, t_last + 1);      // exclusive; may be <= t_begin (empty split)
+    // as even as it goes: the first n_tiles % n_splits splits take one tile more than the others
+    const int per_split = n_tiles / n_splits, longer = n_tiles - per_split * n_splits;
+    const int t_begin = t_first + split * per_split + min(split, longer);
+    const int t_end = t_begin + per_split + (split < longer ? 1 : 0);      // exclusive; == t_begin for an empty split
 
     __nv_bfloat16 new_k_lo[E], new_k_hi[E];
     const bool patches = FUSED && fused.write_cache && t_begin <= t_last && t_last < t_end;
