@@ -11,6 +11,14 @@ weight once, the cache of the live requests) with the measured HBM copy bandwidt
 ``points`` holds batch 1 and 64; ``workloads`` the reference's three public workloads
 (batch x prompt x new tokens) as tokens per second of whole ``generate`` calls, prefill
 included.  Only N=1 is supported.
+
+``--impl reference`` runs the unmodified reference engine (a copy of its ``engine/`` folder
+under ``baseline/_ref/``) through its own ``Engine(model_path).generate`` on the same
+configuration, batch, prompt length and step counts, and prints the same line with
+``"impl": "reference"``.  ``--workload 8b|14b`` runs the two larger workloads: batch 16 with
+prompts of 64 to 2,048 tokens and 128 greedy steps at the Qwen3-8B sizes; batch 64 with
+1,024-token prompts and 256 steps, half of the sequences sampling at temperature 0.8, at the
+Qwen3-14B sizes.
 """
 
 from __future__ import annotations
@@ -27,19 +35,15 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN3_4B = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=2560,
-    intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-    rms_norm_eps=1e-6, rope_theta=5000000.0, tie_word_embeddings=True, max_position_embeddings=4096,
-    hidden_act="silu", attention_bias=False, rope_scaling=None,
-)
-# Other layer sizes of the family, for measurements beside the default run (--sizes).
-OTHER_SIZES = {
-    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
-               num_key_value_heads=8, rope_theta=1000000.0, tie_word_embeddings=False),
-    "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
-                num_key_value_heads=8, rope_theta=1000000.0, tie_word_embeddings=False),
-}
+SIZES = {"4b": "qwen3-4b", "8b": "qwen3-8b", "14b": "qwen3-14b"}     # named configurations of the package
+
+
+def config_json(sizes):
+    """The config.json of the package's named configuration (data under config/presets)."""
+    with open(os.path.join(ROOT, "thing_htn_2026_b200", "config", "presets", SIZES[sizes] + ".json")) as handle:
+        return json.load(handle)
+
+
 CONTEXT = 4096
 PROMPT = 512
 PREFILL_TOKENS = 2048
@@ -135,9 +139,7 @@ def run_ours(args):
     from thing_htn_2026_b200.engine.generation import Request
     from thing_htn_2026_b200.engine.step import StepEntry
 
-    cfg = dict(QWEN3_4B)
-    if args.sizes != "4b":
-        cfg.update(OTHER_SIZES[args.sizes])
+    cfg = config_json(args.sizes)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -315,23 +317,248 @@ def run_ours(args):
     return 0
 
 
+# ----------------------------------------------------------------------------- the larger workloads
+
+LARGE_WORKLOADS = {
+    # sizes, batch, (shortest, longest) prompt, decode steps, temperature of every second sequence
+    "8b": ("8b", 16, (64, 2048), 128, 0.0),
+    "14b": ("14b", 64, (1024, 1024), 256, 0.8),
+}
+
+
+def run_workload(args):
+    """One of the two larger workloads, prefill and decode timed on the device."""
+    import torch
+    from thing_htn_2026_b200 import Engine
+    from thing_htn_2026_b200.config import config_from_dict
+    from thing_htn_2026_b200.engine.generation import Request
+
+    sizes, batch, (shortest, longest), steps, temperature = LARGE_WORKLOADS[args.workload]
+    steps = args.steps if args.steps_given else steps
+    cfg = config_json(sizes)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_layers = cfg["num_hidden_layers"]
+    peak = peaks()
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(shortest, longest + 1, (batch,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    warmup = max(args.warmup, 3)
+    n_new = warmup + steps + 1
+    max_tokens = sum(-(-(n + n_new) // 64) * 64 for n in lens)
+    engine = Engine.from_config(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=max_tokens, max_batch=batch)
+    backend = engine.backend
+    requests = [Request(p, n_new, temperature if i % 2 else 0.0, 1234, i) for i, p in enumerate(prompts)]
+
+    def one_run(timed):
+        slots = backend.open_batch(requests)
+        try:
+            start, mid, end = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            torch.cuda.synchronize()
+            start.record()
+            first = backend.launch_prefill(slots, prompts)
+            mid.record()
+            backend.fetch(first)
+            for _ in range(warmup):
+                backend.fetch(backend.launch_decode(slots))
+            torch.cuda.synchronize()
+            sampler = ClockSampler() if timed else None
+            if sampler:
+                sampler.start()
+                time.sleep(0.3)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            handles = []
+            for _ in range(steps):
+                handles.append(backend.launch_decode(slots))
+                if len(handles) > 3:
+                    backend.fetch(handles.pop(0))
+            t1.record()
+            torch.cuda.synchronize()
+            for h in handles:
+                backend.fetch(h)
+            clocks = sampler.stop() if sampler else None
+            return start.elapsed_time(mid), t0.elapsed_time(t1) / steps, clocks
+        finally:
+            backend.close_batch(slots)
+
+    one_run(False)                                   # captures the graphs, settles the allocator
+    prefill_ms, ms, clocks = one_run(True)
+    numbers = model_numbers(cfg, n_layers)
+    context_mean = sum(lens) / batch + warmup + (steps - 1) / 2.0
+    step_bytes = numbers["weight_bytes"] + batch * context_mean * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = sum(prefill_flops(cfg, n_layers, n) for n in lens)
+    line = {
+        "metric": f"decode tok/s at batch {batch} (Qwen3-{sizes.upper()} layer sizes, random bf16 weights, 1 B200)",
+        "value": batch * 1000.0 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random-init weights, seeded uniform-random token ids", "impl": "ours",
+        "config": {"model": f"Qwen3-{sizes.upper()} layer sizes", "workload": args.workload, "layers": n_layers,
+                   "layers_full": full_layers, "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "tied": bool(cfg["tie_word_embeddings"]), "global_batch": batch, "prompt_min": min(lens),
+                   "prompt_max": max(lens), "prompt_tokens": sum(lens), "context_mean": context_mean,
+                   "sampled_sequences": sum(1 for r in requests if r.temperature > 0), "temperature": temperature,
+                   "parallelism": "single GPU", "peaks": peak["source"]},
+        "prefill": {"value": sum(lens) / (prefill_ms * 1e-3), "tokens": sum(lens), "ms": prefill_ms,
+                    "frac": flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peak["hbm_gbs"], "bytes_per_step": step_bytes},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------- the reference arm
+
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def unavailable(why):
+    print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
+    return 0
+
+
 def run_reference(args):
-    print(json.dumps({
+    """The unmodified reference: its ``engine/`` folder as copied to ``baseline/_ref/engine``,
+    built by its own ``Engine(model_path)`` on a random Qwen3-4B-size folder and driven through
+    its own ``generate(input_ids, max_new_tokens)``.  Nothing of this repository's package is
+    imported into this process: the folder is written by a child process."""
+    engine_dir = os.path.join(REF_DIR, "engine")
+    if not os.path.isfile(os.path.join(engine_dir, "engine.py")):
+        return unavailable(f"no copy of the reference's engine/ folder under baseline/_ref (looked for "
+                           f"{os.path.relpath(engine_dir, ROOT)}/engine.py)")
+    cfg = config_json(args.sizes)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    n_layers = cfg["num_hidden_layers"]
+    warmup = max(args.warmup, 3)
+    folder = tempfile.mkdtemp(prefix="thn_reference_model_")
+    try:
+        made = subprocess.run(
+            [sys.executable, "-m", "thing_htn_2026_b200", "random-model", "--random-config", SIZES[args.sizes],
+             "--layers", str(args.layers), "--seed", "0", "--dtype", "bfloat16", "--device", "cuda:0", "--out", folder],
+            cwd=ROOT, capture_output=True, text=True)
+        if made.returncode != 0:
+            return unavailable(f"could not write the random model folder: {made.stderr.strip()[-300:]}")
+        try:
+            sys.path.insert(0, engine_dir)
+            import torch
+            import engine as reference_engine              # baseline/_ref/engine/engine.py
+            ref = reference_engine.Engine(folder)
+        except Exception as error:  # noqa: BLE001 - whatever stops the reference from starting is the answer
+            return unavailable(f"the reference engine did not start: {type(error).__name__}: {error}")
+        return time_reference(args, ref, torch, cfg, n_layers, full_layers, warmup)
+    finally:
+        import shutil
+        shutil.rmtree(folder, ignore_errors=True)
+
+
+def time_reference(args, ref, torch, cfg, n_layers, full_layers, warmup):
+    peak = peaks()
+    vocab = cfg["vocab_size"]
+    g = torch.Generator().manual_seed(0)
+
+    def prompts(batch, length):
+        return torch.randint(0, vocab, (batch, length), generator=g).tolist()
+
+    def decode(batch, steps, sample_clocks=False):
+        """Wall time between the yields of ``generate`` after ``warmup`` decode steps: host token
+        lists in, host token lists out, as its caller sees them."""
+        n_new = 1 + warmup + steps
+        list(ref.generate(prompts(batch, args.prompt_len), n_new))          # its per-shape preparation and graph capture
+        sampler = ClockSampler() if sample_clocks else None
+        ids = prompts(batch, args.prompt_len)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        stamps = []
+        for i, tokens in enumerate(ref.generate(ids, n_new)):
+            stamps.append(time.perf_counter())
+            if i == warmup and sampler:
+                sampler.start()
+        clocks = sampler.stop() if sampler else None
+        assert len(stamps) == n_new and len(tokens) == batch
+        seconds = stamps[-1] - stamps[warmup]
+        return 1e3 * seconds / steps, 1e3 * (stamps[0] - t0), clocks, batch * n_new / (stamps[-1] - t0)
+
+    started = time.perf_counter()
+    ms, _, clocks, with_prefill = decode(args.batch, args.steps, sample_clocks=True)
+    value = args.batch * 1000.0 / ms
+    numbers = model_numbers(cfg, n_layers)
+    ctx_mean = args.prompt_len + warmup + (args.steps - 1) / 2.0
+    step_bytes = numbers["weight_bytes"] + args.batch * 2 * cfg["hidden_size"] \
+        + args.batch * ctx_mean * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    # time to the first token of one 2,048-token prompt
+    list(ref.generate(prompts(1, PREFILL_TOKENS), 2))
+    times = []
+    for _ in range(3):
+        ids = prompts(1, PREFILL_TOKENS)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for tokens in ref.generate(ids, 1):
+            times.append(1e3 * (time.perf_counter() - t0))
+    prefill_ms = statistics.median(times)
+    flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+
+    points = {}
+    if not args.no_points:
+        for batch in (1, 64):
+            if time.perf_counter() - started > 420:          # each new shape costs the reference a warm-up
+                break
+            pms, _, _, _ = decode(batch, min(args.steps, 64))
+            points[f"decode_b{batch}"] = batch * 1000.0 / pms
+
+    line = {
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.sizes.upper()} layer sizes, random bf16 weights, 1 B200)",
+        "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random-init weights, seeded uniform-random token ids",
         "impl": "reference",
-        "unavailable": "the reference is not an installable package (pip: neither setup.py nor pyproject.toml "
-                       "found), and its engine loads a checkpoint through a library loader that is not a "
-                       "source here",
-    }))
+        "config": {
+            "model": f"Qwen3-{args.sizes.upper()} layer sizes", "layers": n_layers, "layers_full": full_layers,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "tied": bool(cfg["tie_word_embeddings"]),
+            "global_batch": args.batch, "seq_len": max(CONTEXT, args.prompt_len + args.steps + warmup + 1),
+            "prompt_len": args.prompt_len, "context_mean": ctx_mean, "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (a step reads all weights)", "graphs": bool(getattr(ref, "use_graphs", False)),
+            "peaks": peak["source"],
+        },
+        "e2e": {"value": value, "unit": "tok/s", "with_prefill": with_prefill,
+                "h2d_bytes_per_step": args.batch * args.prompt_len * 8 / (1 + warmup + args.steps),
+                "d2h_bytes_per_step": args.batch * 8,
+                "note": "the reference has one public call, generate(): value and e2e are the same wall-clock "
+                        "measurement between its yields (prompt ids uploaded once as int64, one int64 token per "
+                        "sequence read back every step)"},
+        "gpu_launches": None,
+        "triton": bool(getattr(ref, "use_triton", False)),
+        "ops": {name: getattr(fn, "__module__", "?").split(".")[-1] for name, fn in getattr(ref, "ops", {}).items()},
+        "prefill": {"value": PREFILL_TOKENS / (prefill_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": prefill_ms,
+                    "frac": flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12),
+                    "note": "time to the first token of generate(), host to host"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peak["hbm_gbs"], "bytes_per_step": step_bytes},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
     return 0
 
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--steps", type=int, default=None, help="timed decode steps (default 256)")
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--sizes", default="4b", choices=["4b"] + sorted(OTHER_SIZES),
+    parser.add_argument("--sizes", default="4b", choices=sorted(SIZES),
                         help="layer sizes of Qwen3-4B (the default run), -8B or -14B")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the decode steps")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all)")
@@ -340,12 +567,19 @@ def main():
     parser.add_argument("--profiler-range", choices=["decode", "prefill"], default=None,
                         help="bracket the timed decode steps, or the last prefill, with cudaProfilerStart/Stop "
                              "(for ncu --profile-from-start off)")
+    parser.add_argument("--workload", choices=sorted(LARGE_WORKLOADS), default=None,
+                        help="one of the two larger workloads instead of the default run")
     args = parser.parse_args()
+    args.steps_given = args.steps is not None
+    if args.steps is None:
+        args.steps = 256
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload:
+        return run_workload(args)
     return run_ours(args)
 
 

@@ -100,13 +100,13 @@ def prefill_products(args):
     # causal attention of the whole prompt over the cache just written
     tile = ops.ROW_TILE()
     starts = list(range(0, m, tile))
-    rows.tile_row0 = torch.tensor(starts, dtype=torch.int32, device=dev)
-    rows.tile_rows = torch.tensor([min(tile, m - r) for r in starts], dtype=torch.int32, device=dev)
-    rows.n_tiles = len(starts)
+    tiles = ops.RowTiles(torch.tensor(starts, dtype=torch.int32, device=dev),
+                         torch.tensor([min(tile, m - r) for r in starts], dtype=torch.int32, device=dev),
+                         len(starts), tile)
     qs = [torch.randn(m, NQ * D, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
     for view in views:
         view.storage.normal_()
-    us = time_cold(lambda i: ops.attention(qs[i], rows, views[i], NQ, D ** -0.5, None, err), copies, args.reps)
+    us = time_cold(lambda i: ops.attention(qs[i], rows, views[i], NQ, D ** -0.5, None, err, tiles), copies, args.reps)
     flops = 4.0 * NQ * D * m * (m + 1) / 2
     print(f"attention_prefill_m{m}", json.dumps({"own_us": round(us, 2), "tflops": round(flops / us / 1e6, 1)}))
     assert int(err.item()) == 0

@@ -44,8 +44,21 @@ def test_bench_line_has_the_contract_keys():
     assert line["gpu_launches"] > 0
 
 
-def test_bench_refuses_more_than_one_gpu_and_reports_the_reference_arm():
+def test_bench_refuses_more_than_one_gpu():
     code, lines = run_bench("--gpus", "2")
     assert code == 2 and len(lines) == 1
-    code, lines = run_bench("--impl", "reference")
-    assert code == 0 and json.loads(lines[0])["impl"] == "reference" and "unavailable" in json.loads(lines[0])
+
+
+def test_reference_arm_prints_its_line_or_says_why_not():
+    """With a copy of the reference's engine folder under baseline/_ref the arm runs the
+    reference's own Engine on a one-layer model of the same sizes; without it, or if the
+    reference does not start here, it says so in one line and exits 0."""
+    code, lines = run_bench("--impl", "reference", "--layers", "1", "--steps", "4", "--warmup", "3", "--no-points")
+    assert code == 0
+    line = json.loads(lines[-1])
+    assert line["impl"] == "reference"
+    if "unavailable" in line:
+        assert isinstance(line["unavailable"], str) and line["unavailable"]
+    else:
+        assert line["value"] > 0 and line["config"]["layers"] == 1 and line["config"]["layers_full"] == 36
+        assert line["prefill"]["tokens"] == 2048 and line["e2e"]["value"] > 0

@@ -21,3 +21,28 @@ def test_help_runs(capsys):
         cli.main(["--help"])
     assert info.value.code == 0
     assert "generate" in capsys.readouterr().out
+
+
+def test_prompt_lens_and_named_configurations(tmp_path, capsys):
+    import json
+    import os
+    from thing_htn_2026_b200.config import config_from_dict, named_config_json, named_configs
+    assert cli.parse_lens("5, 9,16") == [5, 9, 16]
+    for bad in ("", "3,x", "0,4"):
+        with pytest.raises(SystemExit):
+            cli.parse_lens(bad)
+    prompts = cli.make_prompts_of([1, 23], 512, 7)
+    assert [len(p) for p in prompts] == [1, 23] and prompts == cli.make_prompts_of([1, 23], 512, 7)
+    assert {"tiny-a", "tiny-b", "qwen3-4b", "qwen3-8b", "qwen3-14b"} <= set(named_configs())
+    for name in named_configs():
+        config_from_dict(named_config_json(name))               # every preset passes the typed reader
+    assert config_from_dict(named_config_json("qwen3-14b")).num_attention_heads == 40
+    with pytest.raises(Exception, match="no configuration named"):
+        named_config_json("qwen3-1t")
+    # random-model runs without a device: a folder from a named configuration
+    out = str(tmp_path / "m")
+    assert cli.main(["random-model", "--random-config", "tiny-b", "--seed", "1", "--out", out, "--dtype", "float32"]) == 0
+    assert sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
+    assert json.load(open(os.path.join(out, "config.json")))["num_key_value_heads"] == 1
+    with pytest.raises(SystemExit):
+        cli.main(["random-model", "--out", out])                # neither --config nor --random-config

@@ -27,7 +27,7 @@ def test_head_dim_defaults_and_is_independent():
     raw["head_dim"] = 48                     # wider than hidden / heads, as in the 4B model
     cfg = config_from_dict(raw)
     assert cfg.head_dim == 48
-    q = cfg.plan().layers[0].mixer
+    q = cfg.plan().layers[0].part("mixer")
     assert q.params["head_dim"] == 48 and q.params["scale"] == 48 ** -0.5
 
 
@@ -35,15 +35,15 @@ def test_plan_carries_sizes_names_and_windows():
     cfg = config_from_dict(tiny.config_json("c"))
     plan = cfg.plan()
     assert len(plan.layers) == 4 and [e.layer for e in plan.schedule] == [0, 1, 2, 3]
-    assert [l.mixer.params["window"] for l in plan.layers] == [None, 24, None, 24]
+    assert [l.part("mixer").params["window"] for l in plan.layers] == [None, 24, None, 24]
     layer = plan.layers[2]
-    assert layer.mixer.tensors["q_proj"] == "model.layers.2.self_attn.q_proj.weight"
-    assert layer.ffn.tensors["down_proj"] == "model.layers.2.mlp.down_proj.weight"
-    assert layer.norm_mixer.params == {"size": 80, "eps": 3e-6}
+    assert layer.part("mixer").tensors["q_proj"] == "model.layers.2.self_attn.q_proj.weight"
+    assert layer.part("ffn").tensors["down_proj"] == "model.layers.2.mlp.down_proj.weight"
+    assert layer.part("norm_mixer").params == {"size": 80, "eps": 3e-6}
     assert plan.head.tensors["weight"] == "lm_head.weight"
     tied = config_from_dict(tiny.config_json("a")).plan()
     assert tied.head.tensors["weight"] == "model.embed_tokens.weight"
-    assert layer.mixer.params["position"].params["theta"] == 500000.0
+    assert layer.part("mixer").params["position"].params["theta"] == 500000.0
 
 
 def test_window_keys():
@@ -113,7 +113,7 @@ def test_registry():
 
 def test_schedule_rules():
     part = PartSpec("x")
-    layer = LayerSpec("pre_norm", part, part, part, part)
+    layer = LayerSpec.of("pre_norm", mixer=part, ffn=part, norm_mixer=part, norm_ffn=part)
 
     def plan(schedule):
         return ModelPlan(8, 8, part, (layer, layer), tuple(schedule), part, part, 64)

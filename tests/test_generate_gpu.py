@@ -153,9 +153,28 @@ def test_graphs_on_and_off_agree(tiny_models, dtype):
 def test_random_weights_engine_runs(tiny_models):
     from thing_htn_2026_b200 import Engine
     from thing_htn_2026_b200.config import config_from_dict
-    engine = Engine.from_config(config_from_dict(tiny.config_json("b")), seed=3, dtype="bfloat16")
+    config = config_from_dict(tiny.config_json("b"))
+    engine = Engine.from_config(config, seed=3, dtype="float32", gain_std=0.1)
     tokens, steps = collect(engine, [[1, 2, 3], [4]], 5)
     assert len(steps) == 5 and all(len(t) == 5 for t in tokens)
+    again, _ = collect(Engine.from_config(config, seed=3, dtype="float32", gain_std=0.1), [[1, 2, 3], [4]], 5)
+    other, _ = collect(Engine.from_config(config, seed=4, dtype="float32", gain_std=0.1), [[1, 2, 3], [4]], 5)
+    assert again == tokens, "the same seed draws other weights"
+    assert other != tokens, "another seed draws the same weights"
+    # the weights drawn on the device, written to a folder, give the same tokens through the loader
+    # and are what the plain implementation needs to check them
+    import tempfile
+    from thing_htn_2026_b200.models.decoder import tensor_specs_of_plan
+    from thing_htn_2026_b200.weights import random_tensors_on_device, write_safetensors
+    import json, os
+    drawn = random_tensors_on_device(tensor_specs_of_plan(config.plan()), 3, torch.float32, torch.device("cuda:0"),
+                                     0.02, 0.1)
+    with tempfile.TemporaryDirectory() as folder:
+        write_safetensors(os.path.join(folder, "model.safetensors"), {k: v.cpu() for k, v in drawn.items()})
+        with open(os.path.join(folder, "config.json"), "w") as handle:
+            json.dump(tiny.config_json("b"), handle)
+        for prompt, emitted in zip([[1, 2, 3], [4]], tokens):
+            check_greedy(folder, "float32", prompt, emitted)
 
 
 def test_greedy_across_classes_of_context_length(tiny_models, monkeypatch):

@@ -161,3 +161,28 @@ def test_generate_all_runs_batches_one_after_another():
     assert [len(c.tokens) for c in done] == [3, 2, 4, 1, 2] and all(c.finish_reason == "length" for c in done)
     kinds = [c[0] for c in backend.calls if c[0] in ("open", "close")]
     assert kinds == ["open", "close"] * 3                    # a batch ends before the next one starts
+
+
+@pytest.mark.parametrize("depth", [1, 3, 9])
+def test_never_more_than_depth_plus_one_unfetched_steps(depth):
+    """The device backend's ring of pinned token buffers is sized from this bound."""
+    class Counting(FakeBackend):
+        outstanding = worst = 0
+
+        def launch_prefill(self, slots, prompts):
+            self.outstanding += 1
+            self.worst = max(self.worst, self.outstanding)
+            return super().launch_prefill(slots, prompts)
+
+        def launch_decode(self, slots):
+            self.outstanding += 1
+            self.worst = max(self.worst, self.outstanding)
+            return super().launch_decode(slots)
+
+        def fetch(self, handle):
+            self.outstanding -= 1
+            return super().fetch(handle)
+
+    backend = Counting()
+    run(backend, [Request([1, 2, 3], 40), Request([4], 25)], depth=depth)
+    assert backend.outstanding == 0 and backend.worst == depth + 1

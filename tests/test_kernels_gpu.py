@@ -217,15 +217,13 @@ class PagedFixture:
         cu_dev = torch.tensor(cu, dtype=torch.int32, device=DEV)
         slots_dev = torch.tensor(self.slots, dtype=torch.int32, device=DEV)
         rows = o.step_rows(cu_dev, slots_dev, self.cache.seq_lens, cu[-1], max(counts))
+        rows.tiles = None
         if max(counts) > 1:
-            r0, rn = [], []
-            for start, c in zip(cu, counts):
-                for r in range(0, c, o.ROW_TILE()):
-                    r0.append(start + r)
-                    rn.append(min(o.ROW_TILE(), c - r))
-            rows.tile_row0 = torch.tensor(r0, dtype=torch.int32, device=DEV)
-            rows.tile_rows = torch.tensor(rn, dtype=torch.int32, device=DEV)
-            rows.n_tiles = len(r0)
+            size = o.ROW_TILE()
+            held = [self.cache.length(slot) for slot in self.slots]
+            r0, rn = o.row_tiles_of(counts, held, size)
+            rows.tiles = o.RowTiles(torch.tensor(r0, dtype=torch.int32, device=DEV),
+                                    torch.tensor(rn, dtype=torch.int32, device=DEV), len(r0), size)
         return rows, cu
 
     def advance(self, rows, counts):
@@ -276,9 +274,9 @@ def attention_case(kernel, dtype, n_q, n_kv, D, lengths, new_counts, window, see
     if kernel == "generic":
         got = o.attention_generic(q, rows, fix.kv, n_q, scale, window, err)
     elif kernel == "prefill":
-        got = o.attention_prefill_bf16(q, rows, fix.kv, n_q, scale, window, err)
+        got = o.attention_prefill_bf16(q, rows, rows.tiles, fix.kv, n_q, scale, window, err)
     elif kernel == "tcgen05":
-        got = o.attention_prefill_tcgen05(q, rows, fix.kv, n_q, scale, window, err)
+        got = o.attention_prefill_tcgen05(q, rows, rows.tiles, fix.kv, n_q, scale, window, err)
     elif kernel == "decode_long":
         rows.max_context = max(lengths)           # what the engine knows on the host
         got = o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, window, err)
@@ -462,11 +460,14 @@ def test_qkv_attention_fused_decode_equals_two_kernels(n_q, n_kv, D, window, gai
     attention) gives, bit for bit, the output and the cache of the two separate kernels.
     The lengths put the new token at a page's first row, at its last row and in the middle,
     and make one sequence one token long."""
+    fused_decode_case(n_q, n_kv, D, window, gain_dtype, [129, 64, 1, 300, 77, 640])
+
+
+def fused_decode_case(n_q, n_kv, D, window, gain_dtype, lengths):
     from thing_htn_2026_b200.config.base import PartSpec
     from thing_htn_2026_b200.parts import Runtime, part_class
     o = ops()
     dtype = torch.bfloat16
-    lengths = [129, 64, 1, 300, 77, 640]
     old = [n - 1 for n in lengths]
     fix = PagedFixture(n_kv, D, lengths, dtype, window)
     # the tokens before this step

@@ -50,13 +50,14 @@ def step_context(cache, slots, counts):
     cu_dev = torch.tensor(cu, dtype=torch.int32, device=DEV)
     slots_dev = torch.tensor(slots, dtype=torch.int32, device=DEV)
     rows = ops.step_rows(cu_dev, slots_dev, cache.seq_lens, cu[-1], max(counts))
+    inputs = {}
     if max(counts) > 1:
-        r0 = [s + r for s, c in zip(cu, counts) for r in range(0, c, ops.ROW_TILE())]
-        rn = [min(ops.ROW_TILE(), c - r) for c in counts for r in range(0, c, ops.ROW_TILE())]
-        rows.tile_row0 = torch.tensor(r0, dtype=torch.int32, device=DEV)
-        rows.tile_rows = torch.tensor(rn, dtype=torch.int32, device=DEV)
-        rows.n_tiles = len(r0)
-    return StepContext(rows=rows, cache=cache, err=ops.new_error_word(DEV)), cu
+        # what the attention part asks of the step function for steps of several rows
+        size = ops.ROW_TILE()
+        r0, rn = ops.row_tiles_of(counts, [cache.length(s) for s in slots], size)
+        inputs = {f"row_tiles/{size}/row0": torch.tensor(r0, dtype=torch.int32, device=DEV),
+                  f"row_tiles/{size}/rows": torch.tensor(rn, dtype=torch.int32, device=DEV)}
+    return StepContext(rows=rows, cache=cache, err=ops.new_error_word(DEV), inputs=inputs), cu
 
 
 def finish_step(cache, ctx, slots, counts):
@@ -288,8 +289,8 @@ def define_toy():
                                                "scale": 0.25, "window": None, "qk_norm_eps": None, "position": None},
                                  {k: f"l0.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
             toy = PartSpec("toy_decay", {"hidden_size": h, "decay": self.decay}, {"proj": "l1.proj"})
-            layers = (LayerSpec("pre_norm", attention, ffn(0), norm("l0.n1"), norm("l0.n2")),
-                      LayerSpec("pre_norm", toy, ffn(1), norm("l1.n1"), norm("l1.n2")))
+            layers = (LayerSpec.of("pre_norm", mixer=attention, ffn=ffn(0), norm_mixer=norm("l0.n1"), norm_ffn=norm("l0.n2")),
+                      LayerSpec.of("pre_norm", mixer=toy, ffn=ffn(1), norm_mixer=norm("l1.n1"), norm_ffn=norm("l1.n2")))
             # attention (writes cache 0), toy (state 1), attention again with the same weights
             # reading cache 0, toy again with a state of its own (2)
             schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 0, writes_cache=False),

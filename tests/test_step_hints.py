@@ -24,3 +24,25 @@ def test_context_class_bounds_every_length_of_its_class():
 def test_few_classes_over_a_long_generation():
     seen = {ops.context_class(n)[0] for n in range(1, 200_000, 13)}
     assert len(seen) <= 6, "one captured graph per class and batch size: the classes stay few"
+
+
+def test_row_tiles_cover_every_row_once_fewest_keys_first():
+    counts, held, size = [5, 300, 128, 1], [0, 64, 1000, 7], 128
+    row0, rows = ops.row_tiles_of(counts, held, size)
+    covered = sorted(r for a, n in zip(row0, rows) for r in range(a, a + n))
+    assert covered == list(range(sum(counts))) and max(rows) <= size
+    starts = [0, 5, 305, 433]
+    def keys(a, n):
+        i = max(j for j, s in enumerate(starts) if s <= a)
+        return held[i] + (a - starts[i]) + n
+    seen = [keys(a, n) for a, n in zip(row0, rows)]
+    assert seen == sorted(seen), "the kernels start at the end of the list: longest tiles last"
+    for a, n in zip(row0, rows):                      # a tile never crosses into another sequence
+        i = max(j for j, s in enumerate(starts) if s <= a)
+        assert a + n <= starts[i] + counts[i]
+
+
+def test_counter_buffer_refuses_to_grow():
+    import pytest
+    with pytest.raises(ops.KernelError, match="arrival counters"):
+        ops._counter_buffer(ops.COUNTER_SLOTS + 1, "cpu")

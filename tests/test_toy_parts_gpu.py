@@ -112,8 +112,8 @@ def define_routed_toy():
                               {k: f"l0.{k}" for k in ("gate_proj", "up_proj", "down_proj")})
             routed = PartSpec("toy_routed", {"hidden_size": h, "n_experts": self.n_experts, "expert_size": 2 * h},
                               {k: f"l1.{k}" for k in ("router", "up", "down")})
-            layers = (LayerSpec("pre_norm", attention(0, interpolated, None), swiglu, norm("l0.n1"), norm("l0.n2")),
-                      LayerSpec("pre_norm", attention(1, rope, WINDOW), routed, norm("l1.n1"), norm("l1.n2")))
+            layers = (LayerSpec.of("pre_norm", mixer=attention(0, interpolated, None), ffn=swiglu, norm_mixer=norm("l0.n1"), norm_ffn=norm("l0.n2")),
+                      LayerSpec.of("pre_norm", mixer=attention(1, rope, WINDOW), ffn=routed, norm_mixer=norm("l1.n1"), norm_ffn=norm("l1.n2")))
             return ModelPlan(h, self.vocab_size,
                              PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": h}, {"weight": "emb"}),
                              layers, (ScheduleEntry(0, 0), ScheduleEntry(1, 1)), norm("final"),
@@ -194,3 +194,149 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path):
         for what, got in (("whole", whole), ("tail", tail), ("batches", mixed)):
             assert np.abs(got[name] - want).max() <= 1e-4, f"{what} {name}: {np.abs(got[name] - want).max():.2e}"
     assert len(used) > 1, "the random router sends every row to the same expert: the test shows nothing"
+
+
+# ----------------------------------------------------------------------------- other block arrangements
+
+
+def define_sandwich_toy():
+    """Two block arrangements that live only in this test: one with a third norm (behind the
+    mixer) whose gain is stored as ``w`` of ``1 + w`` and drawn by an initializer registered
+    here, and one that has no feed-forward at all."""
+    from dataclasses import dataclass
+
+    from thing_htn_2026_b200 import ops
+    from thing_htn_2026_b200.config import register_architecture
+    from thing_htn_2026_b200.config.base import LayerSpec, ModelConfig, ModelPlan, PartSpec, ScheduleEntry
+    from thing_htn_2026_b200.config.registry import _decoder_model, known_architectures
+    from thing_htn_2026_b200.parts import Block, register_part
+    from thing_htn_2026_b200.weights import GAIN, INITIALIZERS, TensorSpec, register_initializer
+
+    if "toy_around_zero" not in INITIALIZERS:
+        register_initializer("toy_around_zero", lambda t, gen, matrix_std, gain_std: t.normal_(0.0, gain_std, generator=gen))
+
+    @register_part("norm", "toy_one_plus_rmsnorm")
+    class OnePlusRMSNorm:
+        @classmethod
+        def tensor_specs(cls, spec):
+            return [TensorSpec(spec.tensors["weight"], (spec.params["size"],), GAIN, init="toy_around_zero")]
+
+        def __init__(self, spec, rt):
+            self.eps = spec.params["eps"]
+            self.gain = (1.0 + rt.tensor(spec, "weight").float()).to(rt.tensor(spec, "weight").dtype)
+
+        def forward(self, x):
+            return ops.rmsnorm(x, self.gain, self.eps)
+
+        def add_forward(self, h, d):
+            return ops.add_rmsnorm(h, d, self.gain, self.eps)
+
+    @register_part("block", "toy_sandwich")
+    class SandwichBlock(Block):
+        MEMBERS = {"norm_mixer": "norm", "mixer": "mixer", "norm_after": "norm", "norm_ffn": "norm", "ffn": "ffn"}
+
+        def forward(self, h, d, ctx, entry):
+            n = self.norm_mixer.forward(h) if d is None else self.norm_mixer.add_forward(h, d)
+            a = self.norm_after.forward(self.mixer.forward(n, ctx, entry))
+            n = self.norm_ffn.add_forward(h, a)
+            return h, self.ffn.forward(n, ctx)
+
+    @register_part("block", "toy_mixer_only")
+    class MixerOnlyBlock(Block):
+        MEMBERS = {"norm_mixer": "norm", "mixer": "mixer"}
+
+        def forward(self, h, d, ctx, entry):
+            n = self.norm_mixer.forward(h) if d is None else self.norm_mixer.add_forward(h, d)
+            return h, self.mixer.forward(n, ctx, entry)
+
+    @dataclass(frozen=True)
+    class SandwichToyConfig(ModelConfig):
+        vocab_size: int
+        hidden_size: int
+        architecture = "SandwichToyForCausalLM"
+
+        @classmethod
+        def from_dict(cls, data):
+            return cls(data["vocab_size"], data["hidden_size"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
+
+        def plan(self):
+            h = self.hidden_size
+
+            def norm(name):
+                return PartSpec("rmsnorm", {"size": h, "eps": 1e-5}, {"weight": name})
+
+            def attention(i):
+                return PartSpec("attention", {"hidden_size": h, "n_heads": N_HEADS, "n_kv_heads": N_KV, "head_dim": HEAD_DIM,
+                                              "scale": HEAD_DIM ** -0.5, "window": None, "qk_norm_eps": None,
+                                              "position": PartSpec("rope", {"head_dim": HEAD_DIM, "theta": 10000.0})},
+                                {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
+
+            layers = (
+                LayerSpec.of("toy_sandwich", mixer=attention(0), norm_mixer=norm("l0.n1"), norm_ffn=norm("l0.n2"),
+                             norm_after=PartSpec("toy_one_plus_rmsnorm", {"size": h, "eps": 1e-5}, {"weight": "l0.after"}),
+                             ffn=PartSpec("swiglu", {"hidden_size": h, "intermediate_size": 2 * h},
+                                          {k: f"l0.{k}" for k in ("gate_proj", "up_proj", "down_proj")})),
+                LayerSpec.of("toy_mixer_only", mixer=attention(1), norm_mixer=norm("l1.n1")),
+            )
+            return ModelPlan(h, self.vocab_size,
+                             PartSpec("embedding", {"vocab_size": self.vocab_size, "hidden_size": h}, {"weight": "emb"}),
+                             layers, (ScheduleEntry(0, 0), ScheduleEntry(1, 1)), norm("final"),
+                             PartSpec("lm_head", {"vocab_size": self.vocab_size, "hidden_size": h, "tied": False},
+                                      {"weight": "head"}), 1024, ignored_tensors=("*.running_stat",))
+
+    if "SandwichToyForCausalLM" not in known_architectures():
+        register_architecture("SandwichToyForCausalLM", SandwichToyConfig, _decoder_model)
+    return SandwichToyConfig
+
+
+def sandwich_toy_plain_logits(folder, tokens):
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    f32 = torch.float32
+    S = len(tokens)
+    cos, sin = plain.rope_cos_sin(torch.arange(S), HEAD_DIM, 10000.0, f32)
+    h = w["emb"][torch.tensor(tokens)]
+
+    def attention(n, i):
+        q = plain.linear(n, w[f"l{i}.q_proj"], f32).reshape(S, N_HEADS, HEAD_DIM)
+        k = plain.linear(n, w[f"l{i}.k_proj"], f32).reshape(S, N_KV, HEAD_DIM)
+        v = plain.linear(n, w[f"l{i}.v_proj"], f32).reshape(S, N_KV, HEAD_DIM)
+        q, k = plain.apply_rope(q, cos, sin, f32), plain.apply_rope(k, cos, sin, f32)
+        a = plain.attention(q, k, v, HEAD_DIM ** -0.5, None, f32).reshape(S, N_HEADS * HEAD_DIM)
+        return plain.linear(a, w[f"l{i}.o_proj"], f32)
+
+    a = attention(plain.rms_norm(h, w["l0.n1"], 1e-5, f32), 0)
+    h = h + plain.rms_norm(a, 1.0 + w["l0.after"], 1e-5, f32)
+    n = plain.rms_norm(h, w["l0.n2"], 1e-5, f32)
+    g, u = plain.linear(n, w["l0.gate_proj"], f32), plain.linear(n, w["l0.up_proj"], f32)
+    h = h + plain.linear(plain.swiglu(g, u, f32), w["l0.down_proj"], f32)
+    h = h + attention(plain.rms_norm(h, w["l1.n1"], 1e-5, f32), 1)
+    return (plain.rms_norm(h, w["final"], 1e-5, f32) @ w["head"].t()).numpy()
+
+
+def test_blocks_with_a_third_norm_and_without_a_feed_forward(tmp_path):
+    """The model above sees blocks only: these two arrangements, their tensors (one with an
+    initializer of its own), their cache needs and the buffer their checkpoint carries are
+    all the test's; no file of the library changes."""
+    Config = define_sandwich_toy()
+    from thing_htn_2026_b200.weights import Checkpoint, write_random_model, write_safetensors
+    folder = write_random_model(str(tmp_path / "sandwich"), Config(90, 48), seed=5, gain_std=0.1)
+    stored = Checkpoint(folder)
+    tensors = {name: stored.read(name) for name in stored.names()}
+    assert abs(tensors["l0.after"].mean().item()) < 0.05 and abs(tensors["l0.n1"].mean().item() - 1) < 0.05
+    assert not any(name.startswith("l1.gate") or name.startswith("l1.n2") for name in tensors)
+    tensors["l0.mixer.running_stat"] = torch.ones(3)           # a buffer the plan says to pass over
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    requests = {f"r{i}": torch.randint(0, 90, (n,), generator=torch.Generator().manual_seed(60 + i)).tolist()
+                for i, n in enumerate([25, 6, 41, 70])}
+    whole = harness.replay(folder, "float32", harness.trace_whole(requests), str(tmp_path / "w"))
+    tail = harness.replay(folder, "float32", harness.trace_tail(requests, 8), str(tmp_path / "t"))
+    batches = [{k: requests[k] for k in ("r0", "r1")}, {k: requests[k] for k in ("r2", "r3")}]
+    mixed = harness.replay(folder, "float32", harness.trace_batches(batches, {"r0": 5, "r1": 6, "r2": 1, "r3": 64}),
+                           str(tmp_path / "b"), max_tokens=192)
+    for name, toks in requests.items():
+        want = sandwich_toy_plain_logits(folder, toks)
+        for what, got in (("whole", whole), ("tail", tail), ("batches", mixed)):
+            assert np.abs(got[name] - want).max() <= 1e-4, f"{what} {name}: {np.abs(got[name] - want).max():.2e}"

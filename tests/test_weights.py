@@ -12,7 +12,8 @@ import tiny
 from plain import qwen3_plain as plain
 from thing_htn_2026_b200.config import config_from_dict
 from thing_htn_2026_b200.models.decoder import tensor_specs_of_plan
-from thing_htn_2026_b200.weights import (GAIN, MATRIX, Checkpoint, SafetensorsError, TensorSpec, WeightError,
+from thing_htn_2026_b200.weights import (GAIN, MATRIX, Checkpoint, SafetensorsError, TensorSpec,
+                                         UndeclaredTensorsWarning, WeightError,
                                          held_dtype, load_tensors, random_tensors_cpu, write_random_model,
                                          write_safetensors)
 
@@ -85,14 +86,77 @@ def test_one_error_lists_everything(tmp_path, tiny_models):
         assert needle in text
 
 
-def test_tied_head_needs_no_head_tensor_and_rejects_a_stray_one(tmp_path, tiny_models):
-    good = Checkpoint(tiny_models["a"])
+def hand_written_folder(tmp_path, source, change):
+    """A folder that this library did not write: the tensors of ``source``, changed by hand."""
+    good = Checkpoint(source)
     tensors = {name: good.read(name) for name in good.names()}
-    assert "lm_head.weight" not in tensors
-    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    change(tensors)
     write_safetensors(str(tmp_path / "model.safetensors"), tensors)
-    with pytest.raises(WeightError, match="unexpected tensors"):
-        load_tensors(str(tmp_path), specs_of("a"), torch.float32, CPU)
+    return str(tmp_path)
+
+
+def test_tied_head_needs_no_head_tensor_and_accepts_a_stored_copy(tmp_path, tiny_models, recwarn):
+    plan = config_from_dict(tiny.config_json("a")).plan()
+    assert "lm_head.weight" not in Checkpoint(tiny_models["a"]).names()
+
+    def add_copy(tensors):
+        tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+
+    folder = hand_written_folder(tmp_path, tiny_models["a"], add_copy)
+    got = load_tensors(folder, specs_of("a"), torch.float32, CPU, ignored=plan.ignored_tensors, strict=True)
+    assert "lm_head.weight" not in got and not recwarn.list      # an equal copy: accepted in silence, even strictly
+
+
+def test_a_stored_head_that_differs_from_the_tied_embedding_is_reported(tmp_path, tiny_models):
+    def add_other(tensors):
+        tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"] + 1.0
+
+    folder = hand_written_folder(tmp_path, tiny_models["a"], add_other)
+    with pytest.warns(UndeclaredTensorsWarning, match="lm_head.weight is stored beside model.embed_tokens.weight"):
+        got = load_tensors(folder, specs_of("a"), torch.float32, CPU)
+    assert torch.equal(got["model.embed_tokens.weight"], Checkpoint(tiny_models["a"]).read("model.embed_tokens.weight"))
+
+    def add_misshapen(tensors):
+        tensors["lm_head.weight"] = torch.zeros(3, 3)
+
+    (tmp_path / "b").mkdir()
+    folder = hand_written_folder(tmp_path / "b", tiny_models["a"], add_misshapen)
+    with pytest.raises(WeightError, match="wrong shapes"):
+        load_tensors(folder, specs_of("a"), torch.float32, CPU)
+
+
+def test_undeclared_tensors_warn_once_and_buffers_pass_in_silence(tmp_path, tiny_models, recwarn):
+    plan = config_from_dict(tiny.config_json("b")).plan()
+
+    def add_extras(tensors):
+        tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16)     # a writer's buffer
+        tensors["model.layers.7.extra.weight"] = torch.zeros(1)
+        tensors["adapter.scale"] = torch.zeros(2)
+
+    folder = hand_written_folder(tmp_path, tiny_models["b"], add_extras)
+    with pytest.warns(UndeclaredTensorsWarning) as caught:
+        got = load_tensors(folder, specs_of("b"), torch.float32, CPU, ignored=plan.ignored_tensors)
+    assert len(caught) == 1
+    text = str(caught[0].message)
+    assert "2 tensors that no part of the model reads" in text
+    assert "model.layers.7.extra.weight" in text and "adapter.scale" in text and "inv_freq" not in text
+    assert set(got) == {s.name for s in specs_of("b")}
+    with pytest.raises(WeightError, match=r"unexpected tensors \(2\)"):
+        load_tensors(folder, specs_of("b"), torch.float32, CPU, ignored=plan.ignored_tensors, strict=True)
+
+
+def test_initializer_rules_by_name():
+    from thing_htn_2026_b200.weights import INITIALIZERS, register_initializer
+    from thing_htn_2026_b200.weights.random_init import _draw
+    g = torch.Generator().manual_seed(3)
+    bias = _draw(TensorSpec("b", (64,), GAIN, init="zeros"), g, "cpu", 0.02, 0.1, torch.float32)
+    assert bias.abs().max() == 0                                   # a role's default can be overridden per tensor
+    if "test_small_gain" not in INITIALIZERS:
+        register_initializer("test_small_gain", lambda t, gen, matrix_std, gain_std: t.normal_(0, gain_std, generator=gen))
+    w = _draw(TensorSpec("w", (4096,), GAIN, init="test_small_gain"), g, "cpu", 0.02, 0.1, torch.float32)
+    assert abs(w.mean().item()) < 0.02 and 0.05 < w.std().item() < 0.15      # a gain stored as w of (1 + w)
+    with pytest.raises(KeyError, match="no initializer named"):
+        _draw(TensorSpec("x", (2,), MATRIX, init="nope"), g, "cpu", 0.02, 0.1, torch.float32)
 
 
 def test_broken_files(tmp_path):

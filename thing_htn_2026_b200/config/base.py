@@ -61,13 +61,25 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: which block arrangement, and the four parts it is made of."""
+    """One decoder layer: a part of the ``block`` family.  The block owns its sub-parts:
+    its ``params`` hold their specs (for the ``pre_norm`` arrangement: ``mixer``, ``ffn``,
+    ``norm_mixer``, ``norm_ffn``), so an arrangement with other members (a third norm, no
+    feed-forward, two mixers side by side) is a new block class and nothing else."""
 
-    block: str            # arrangement of the parts, e.g. "pre_norm"
-    mixer: PartSpec       # token mixer (attention here)
-    ffn: PartSpec         # feed-forward (dense here)
-    norm_mixer: PartSpec  # norm in front of the mixer
-    norm_ffn: PartSpec    # norm in front of the feed-forward
+    block: PartSpec
+
+    @classmethod
+    def of(cls, kind: str, **parts: Any) -> "LayerSpec":
+        """``LayerSpec.of("pre_norm", mixer=..., ffn=..., norm_mixer=..., norm_ffn=...)``: a
+        block of that kind whose parameters are the given sub-part specs (and constants)."""
+        return cls(PartSpec(kind, parts))
+
+    def part(self, name: str) -> PartSpec:
+        """A sub-part's spec by its name among the block's parameters."""
+        value = self.block.params.get(name)
+        if not isinstance(value, PartSpec):
+            raise KeyError(f"block '{self.block.kind}' has no part named '{name}'")
+        return value
 
 
 @dataclass(frozen=True)
@@ -96,6 +108,9 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     max_positions: int
+    # Name patterns (fnmatch) of checkpoint tensors that no part reads and the loader passes
+    # over in silence: buffers that some writers store beside the weights.
+    ignored_tensors: Tuple[str, ...] = ()
 
     def __post_init__(self):
         n_layers = len(self.layers)

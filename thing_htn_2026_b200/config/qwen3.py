@@ -198,8 +198,8 @@ class Qwen3Config(ModelConfig):
                     "down_proj": f"{prefix}.mlp.down_proj.weight",
                 },
             )
-            layers.append(LayerSpec(
-                block="pre_norm",
+            layers.append(LayerSpec.of(
+                "pre_norm",
                 mixer=mixer,
                 ffn=ffn,
                 norm_mixer=PartSpec("rmsnorm", {"size": hidden, "eps": eps},
@@ -219,6 +219,10 @@ class Qwen3Config(ModelConfig):
             head=PartSpec("lm_head",
                           {"vocab_size": self.vocab_size, "hidden_size": hidden,
                            "tied": self.tie_word_embeddings},
-                          {"weight": embed_name if self.tie_word_embeddings else "lm_head.weight"}),
+                          # A tied head reads the embedding table; some writers store the head a
+                          # second time under its own name, which the loader then compares.
+                          {"weight": embed_name, "stored_copy": "lm_head.weight"} if self.tie_word_embeddings
+                          else {"weight": "lm_head.weight"}),
             max_positions=self.max_position_embeddings,
+            ignored_tensors=("*.rotary_emb.inv_freq",),
         )

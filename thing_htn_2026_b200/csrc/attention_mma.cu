@@ -845,12 +845,17 @@ int decode_clusters_resident(int c) {
     return resident[c];
 }
 
+// What the last launch of the decode kernel was built with: tile buffers * 10 + 1 if the splits
+// met in a cluster.  Tests read it to see that they reached the variant they mean to check.
+int g_last_decode_variant = 0;
+
 template <int D, int STAGES, bool FUSED, bool CLUSTER>
 int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                        PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
                        cudaStream_t stream, const FusedInput& fused) {
     int configured = configure_decode<D, STAGES, FUSED, CLUSTER>();
     if (configured != THN_OK) return configured;
+    g_last_decode_variant = STAGES * 10 + (CLUSTER ? 1 : 0);
     dim3 grid(n_seqs, kv.n_kv, n_splits);
     if (CLUSTER)      // the splits of a (sequence, kv head) as one cluster along z
         thn_launch_cluster(attention_decode_kernel<D, STAGES, FUSED, CLUSTER>, grid, kThreads, decode_smem<D, STAGES>(),
@@ -902,6 +907,9 @@ THN_API int thn_attention_mma_supported(int head_dim, int page_size, int n_q, in
     return (head_dim == 64 || head_dim == 128) && page_size == kTile && n_kv > 0 && n_q % n_kv == 0 &&
            n_q / n_kv <= 16;
 }
+
+// Tile buffers * 10 + (1: cluster) of the most recent decode attention launch of this process.
+THN_API int thn_attention_decode_last_variant() { return g_last_decode_variant; }
 
 // Rows of a row tile of the prompt kernel (see thn_attention_prefill_bf16).
 THN_API int thn_attention_prefill_tile_rows() { return kPrefillRows; }

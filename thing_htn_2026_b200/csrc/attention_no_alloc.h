@@ -36,7 +36,15 @@
 
 #define THN_NO_ALLOC_SCRATCH_FLOATS (1 << 20)
 
-extern "C" __attribute__((visibility("default"))) int thn_attention_decode_bf16_no_alloc(
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+__attribute__((visibility("default"))) int thn_attention_decode_bf16_no_alloc(
     void* out, const void* q, const int* row_slot, const int* row_pos, const void* kv_base, const int* block_table,
     int bt_stride, int n_kv, int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale, int window,
     int* err, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -21,6 +21,7 @@ import torch
 from .. import ops
 from ..cache.sequence_cache import SequenceCache
 from ..parts import StepContext
+from ..sampling import TokenChooser
 from .generation import Request, tokens_needed
 from .step import StepEntry, StepRunner
 
@@ -30,11 +31,15 @@ class _Handle:
     buffer: torch.Tensor     # pinned int32
     event: torch.cuda.Event
     count: int
+    place: int               # in the ring
 
 
 class DeviceBackend:
     def __init__(self, model, cache: SequenceCache, *, max_batch: int = 64, use_graphs: bool = True,
                  ring: int = 8):
+        """``ring``: pinned token buffers for steps whose tokens the host has not fetched yet;
+        a generation loop of depth d keeps d + 1 such steps, so it needs ``ring >= d + 1``.
+        Sending one more than the ring holds raises instead of overwriting."""
         self.model, self.cache = model, cache
         self.device = model.device
         self.page_size = cache.page_size
@@ -42,12 +47,8 @@ class DeviceBackend:
         self.use_graphs = bool(use_graphs)
         self.runner = StepRunner(model, cache)
         self.err = self.runner.err
-        state = cache.sequence_state
-        self.last_token = state("last_token", (), torch.int32)
-        self.sample_step = state("sample_step", (), torch.int32)
-        self.temperature = state("temperature", (), torch.float32)
-        self.seed = state("seed", (), torch.int64)
-        self.stream_id = state("stream", (), torch.int32)
+        self.chooser = TokenChooser(cache)
+        self.last_token = self.chooser.last_token
 
         n = self._max_batch
         dev = self.device
@@ -59,11 +60,13 @@ class DeviceBackend:
         self.row_pos = torch.zeros(n, dtype=torch.int32, device=dev)
         self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}     # (batch, context class)
         self._composition: Optional[Tuple[int, ...]] = None
+        ring = max(2, int(ring))
         self._ring = [(torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
                       for _ in range(ring)]
+        self._ring_busy = [False] * ring          # sent and not fetched yet
         self._stage = [torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True) for _ in range(ring)]
         self._ring_next = 0
-        self._sampling = False
+        self.graph_logits: Dict[Tuple[int, int], torch.Tensor] = {}    # the captured programs' logits
         # One slot with one page stays reserved: decode graphs are warmed up on it.
         (self._scratch_slot,) = cache.open(1)
         cache.prepare([self._scratch_slot], [1])
@@ -86,14 +89,8 @@ class DeviceBackend:
         except Exception:
             self.cache.close(slots)
             raise
-        index = torch.tensor(slots, dtype=torch.int64, device=self.device)
-        self.temperature.index_copy_(0, index, torch.tensor([r.temperature for r in requests], dtype=torch.float32,
-                                                            device=self.device))
-        self.seed.index_copy_(0, index, torch.tensor([_as_i64(r.seed) for r in requests], dtype=torch.int64,
-                                                     device=self.device))
-        self.stream_id.index_copy_(0, index, torch.tensor([r.stream & 0x7FFFFFFF for r in requests],
-                                                          dtype=torch.int32, device=self.device))
-        self._sampling = any(r.temperature > 0 for r in requests)
+        self.chooser.configure(slots, [r.temperature for r in requests], [r.seed for r in requests],
+                               [r.stream for r in requests])
         self._composition = None
         return slots
 
@@ -103,39 +100,38 @@ class DeviceBackend:
 
     # ------------------------------------------------------------------ steps
 
-    def _choose(self, logits: torch.Tensor, slots_dev: torch.Tensor, out: torch.Tensor) -> None:
-        ops.choose_tokens(logits, self.temperature, self.seed, self.stream_id, self.sample_step, out=out,
-                          slots=slots_dev, last_token=self.last_token, bump_step=True)
-
     def _send(self, tokens_dev: torch.Tensor, count: int) -> _Handle:
-        buffer, event = self._ring[self._ring_next]
-        self._ring_next = (self._ring_next + 1) % len(self._ring)
+        at = self._ring_next
+        if self._ring_busy[at]:
+            raise RuntimeError(f"{len(self._ring) + 1} steps are in flight whose tokens the host has not fetched; "
+                               f"the backend was built with a ring of {len(self._ring)}")
+        buffer, event = self._ring[at]
+        self._ring_next = (at + 1) % len(self._ring)
+        self._ring_busy[at] = True
         buffer[:count].copy_(tokens_dev[:count], non_blocking=True)
         event.record()
-        return _Handle(buffer, event, count)
+        return _Handle(buffer, event, count, at)
 
     def launch_prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> _Handle:
         entries = [StepEntry(slot, prompt, (len(prompt) - 1,)) for slot, prompt in zip(slots, prompts)]
         logits = self.runner.step(entries, check=False)
         slots_dev = self.runner._upload(list(slots))
         out = torch.empty(len(slots), dtype=torch.int32, device=self.device)
-        self._choose(logits, slots_dev, out)
+        self.chooser.choose(logits, slots_dev, out)
         return self._send(out, len(slots))
 
-    def _decode_program(self, batch: int, max_context: int) -> None:
-        """One token for each of the first ``batch`` slots of ``slots_buf``; everything it
-        reads and writes is per-sequence state or a static buffer.  ``max_context`` bounds
-        the keys a sequence holds after the step, for as long as the program is replayed."""
+    def _decode_program(self, batch: int, max_context: int) -> torch.Tensor:
+        """One token for each of the first ``batch`` slots of ``slots_buf``: the step function's
+        device side (``StepRunner.run_rows``) between a gather of each sequence's last token
+        and the token choice.  Everything it reads and writes is per-sequence state or a
+        static buffer.  ``max_context`` bounds the keys a sequence holds after the step, for
+        as long as the program is replayed.  Returns the step's logits."""
         slots = self.slots_buf[:batch]
-        cu = self.cu_buf[:batch + 1]
         tokens = ops.gather_i32(self.last_token, slots, out=self.tokens_in[:batch])
-        rows = ops.step_rows(cu, slots, self.cache.seq_lens, batch, 1,
-                             out=(self.row_slot[:batch], self.row_pos[:batch]), max_context=max_context)
-        ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
-        h, d = self.model.hidden(tokens, ctx)
-        logits = self.model.logits(h, d, None, self.err)
-        self._choose(logits, slots, self.out_tokens[:batch])
-        ops.advance(self.cache.seq_lens, slots, cu)
+        logits = self.runner.run_rows(tokens, self.cu_buf[:batch + 1], slots, batch, 1, max_context, None,
+                                      row_out=(self.row_slot[:batch], self.row_pos[:batch]))
+        self.chooser.choose(logits, slots, self.out_tokens[:batch])
+        return logits
 
     def _set_composition(self, slots: Sequence[int]) -> None:
         key = tuple(slots)
@@ -162,7 +158,7 @@ class DeviceBackend:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self._decode_program(batch, max_context)
+            self.graph_logits[(batch, context_class)] = self._decode_program(batch, max_context)
         self.cache.seq_lens[self._scratch_slot] = 0
         torch.cuda.synchronize()
         self.graphs[(batch, context_class)] = graph
@@ -183,9 +179,6 @@ class DeviceBackend:
 
     def fetch(self, handle: _Handle) -> List[int]:
         handle.event.synchronize()
-        return handle.buffer[:handle.count].tolist()
-
-
-def _as_i64(seed: int) -> int:
-    seed &= 0xFFFFFFFFFFFFFFFF
-    return seed - (1 << 64) if seed >= (1 << 63) else seed
+        tokens = handle.buffer[:handle.count].tolist()
+        self._ring_busy[handle.place] = False
+        return tokens

@@ -68,7 +68,8 @@ class Engine:
         pages = -(-max_tokens // page) + 1          # one page for the backend's scratch slot
         cache = SequenceCache(self.model.cache_needs(), max_tokens=pages * page, dtype=self.dtype,
                               device=self.device, max_slots=max(2, min(pages, self.max_batch + 1)))
-        self.backend = DeviceBackend(self.model, cache, max_batch=self.max_batch, use_graphs=self.use_graphs)
+        self.backend = DeviceBackend(self.model, cache, max_batch=self.max_batch, use_graphs=self.use_graphs,
+                                     ring=self.depth + 2)
         self.loop = GenerationLoop(self.backend, self.depth)
 
     def _ensure_cache(self, requests: Sequence[Request], whole_queue_in_one_batch: bool) -> None:

@@ -13,13 +13,13 @@ The reference has two functions with equal lengths only: ``_prefill_slice`` for 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .. import ops
 from ..cache.sequence_cache import SequenceCache
-from ..parts import StepContext
+from ..parts import HostBatch, StepContext
 
 
 @dataclass
@@ -60,6 +60,25 @@ class StepRunner:
         self.uploaded_bytes += 4 * n
         return device
 
+    def run_rows(self, tokens: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, n_rows: int,
+                 max_q_len: int, max_context: Optional[int], want_rows: Optional[torch.Tensor],
+                 inputs: Optional[Dict[str, torch.Tensor]] = None,
+                 row_out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
+        """The device side of a step, and the only forward pass there is: rows and positions
+        from the sequences' lengths, the scheduled layers from the cache, final norm and head
+        at ``want_rows`` (int32 row indices; None: every row; empty: none, returns None),
+        lengths advanced.  Every argument lives on the device and nothing here synchronises,
+        so the same call is recorded into the generation loop's decode graphs."""
+        rows = ops.step_rows(cu_seqlens, slots, self.cache.seq_lens, n_rows, max_q_len, out=row_out,
+                             max_context=max_context)
+        ctx = StepContext(rows=rows, cache=self.cache, err=self.err, inputs=inputs or {})
+        h, d = self.model.hidden(tokens, ctx)
+        logits = None
+        if want_rows is None or want_rows.shape[0]:
+            logits = self.model.logits(h, d, want_rows, self.err)
+        ops.advance(self.cache.seq_lens, slots, cu_seqlens)
+        return logits
+
     def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
         """Runs the entries' tokens; returns float32 logits ``[wanted, vocab]`` in the order
         of the entries and of their ``want``.  Raises CacheFull before touching anything if
@@ -80,43 +99,24 @@ class StepRunner:
                     raise ValueError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} tokens")
                 want_rows.append(start + w)
         self.cache.prepare(slots, counts)
+        held = [self.cache.length(slot) for slot in slots]
 
-        tile_row0: List[int] = []
-        tile_rows: List[int] = []
-        if max(counts) > 1:
-            # Row tiles for the prompt attention kernels, the ones that see the fewest keys
-            # first: the kernels start at the end of the list, so the longest run first and
-            # the short ones fill the gaps at the end.
-            size = ops.ROW_TILE()
-            tiles = []
-            for slot, start, c in zip(slots, cu, counts):
-                held = self.cache.length(slot)
-                for r in range(0, c, size):
-                    n = min(size, c - r)
-                    tiles.append((held + r + n, start + r, n))
-            tiles.sort()
-            tile_row0 = [t[1] for t in tiles]
-            tile_rows = [t[2] for t in tiles]
-
-        parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows, tile_row0, tile_rows]
+        # What parts want computed on the host for this step travels with the tokens.
+        asked = self.model.step_inputs(HostBatch(slots, counts, held, self.cache.page_size))
+        names = sorted(asked)
+        parts = [[t for e in entries for t in e.tokens], cu, slots, want_rows] + [list(asked[n]) for n in names]
         packed = self._upload([x for part in parts for x in part])
         views, at = [], 0
         for part in parts:
             views.append(packed[at:at + len(part)])
             at += len(part)
-        tokens, cu_dev, slots_dev, want_dev, tile_row0_dev, tile_rows_dev = views
+        tokens, cu_dev, slots_dev, want_dev = views[:4]
+        inputs = dict(zip(names, views[4:]))
 
-        longest = max(self.cache.length(slot) + c for slot, c in zip(slots, counts))
-        rows = ops.step_rows(cu_dev, slots_dev, self.cache.seq_lens, n_rows, max(counts), max_context=longest)
-        if tile_row0:
-            rows.tile_row0, rows.tile_rows, rows.n_tiles = tile_row0_dev, tile_rows_dev, len(tile_row0)
-        ctx = StepContext(rows=rows, cache=self.cache, err=self.err)
-        h, d = self.model.hidden(tokens, ctx)
-        if want_rows:
-            logits = self.model.logits(h, d, want_dev, self.err)
-        else:
+        longest = max(h + c for h, c in zip(held, counts))
+        logits = self.run_rows(tokens, cu_dev, slots_dev, n_rows, max(counts), longest, want_dev, inputs)
+        if logits is None:
             logits = torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
-        ops.advance(self.cache.seq_lens, slots_dev, cu_dev)
         self.cache.commit(slots, counts)
         if check:
             ops.raise_on_device_error(self.err, "step")

@@ -12,7 +12,7 @@ import torch
 from .. import ops
 from ..cache.sequence_cache import CacheNeed
 from ..config.base import ModelConfig, ModelPlan, PartSpec
-from ..parts import Runtime, StepContext, part_class
+from ..parts import HostBatch, Runtime, StepContext, part_class
 from ..weights.loader import TensorSpec, load_tensors, merge_specs
 from ..weights.random_init import random_tensors_on_device
 
@@ -21,10 +21,7 @@ def tensor_specs_of_plan(plan: ModelPlan) -> List[TensorSpec]:
     """Every tensor the plan's parts declare, in declaration order."""
     specs: List[TensorSpec] = list(part_class("embedding", plan.embedding.kind).tensor_specs(plan.embedding))
     for layer in plan.layers:
-        specs += part_class("norm", layer.norm_mixer.kind).tensor_specs(layer.norm_mixer)
-        specs += part_class("mixer", layer.mixer.kind).tensor_specs(layer.mixer)
-        specs += part_class("norm", layer.norm_ffn.kind).tensor_specs(layer.norm_ffn)
-        specs += part_class("ffn", layer.ffn.kind).tensor_specs(layer.ffn)
+        specs += part_class("block", layer.block.kind).tensor_specs(layer.block)
     specs += part_class("norm", plan.final_norm.kind).tensor_specs(plan.final_norm)
     specs += part_class("head", plan.head.kind).tensor_specs(plan.head)
     return specs
@@ -40,13 +37,7 @@ class DecoderModel:
             raise ops.KernelError(f"the model runs on CUDA only, got device {self.device}")
         self.runtime = runtime = Runtime(dtype, self.device, tensors)
         self.embedding = part_class("embedding", plan.embedding.kind)(plan.embedding, runtime)
-        self.layers = []
-        for layer in plan.layers:
-            self.layers.append(part_class("block", layer.block)(
-                part_class("mixer", layer.mixer.kind)(layer.mixer, runtime),
-                part_class("ffn", layer.ffn.kind)(layer.ffn, runtime),
-                part_class("norm", layer.norm_mixer.kind)(layer.norm_mixer, runtime),
-                part_class("norm", layer.norm_ffn.kind)(layer.norm_ffn, runtime)))
+        self.layers = [part_class("block", layer.block.kind)(layer.block, runtime) for layer in plan.layers]
         self.final_norm = part_class("norm", plan.final_norm.kind)(plan.final_norm, runtime)
         self.head = part_class("head", plan.head.kind)(plan.head, runtime)
         self.vocab_size = plan.vocab_size
@@ -56,7 +47,9 @@ class DecoderModel:
 
     @classmethod
     def from_folder(cls, config: ModelConfig, model_dir: str, dtype: torch.dtype, device) -> "DecoderModel":
-        tensors = load_tensors(model_dir, tensor_specs_of_plan(config.plan()), dtype, torch.device(device))
+        plan = config.plan()
+        tensors = load_tensors(model_dir, tensor_specs_of_plan(plan), dtype, torch.device(device),
+                               ignored=plan.ignored_tensors)
         return cls(config, tensors, dtype, device)
 
     @classmethod
@@ -73,13 +66,21 @@ class DecoderModel:
         needs: List[CacheNeed] = [None] * self.plan.n_cache_entries
         for entry in self.plan.schedule:
             if entry.writes_cache:
-                needs[entry.cache] = self.layers[entry.layer].mixer.cache_need()
+                needs[entry.cache] = self.layers[entry.layer].cache_need()
         return needs
 
     def ensure_positions(self, n_positions: int) -> None:
         for part in self.runtime.shared.values():
             if hasattr(part, "ensure"):
                 part.ensure(n_positions)
+
+    def step_inputs(self, batch: HostBatch) -> Dict[str, List[int]]:
+        """Integer inputs that parts want computed on the host for this step, by name; the
+        step function uploads them with the tokens."""
+        out: Dict[str, List[int]] = {}
+        for layer in self.layers:
+            layer.step_inputs(batch, out)
+        return out
 
     # ------------------------------------------------------------------ forward
 

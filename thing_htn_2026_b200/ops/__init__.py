@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 import os
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -69,6 +69,7 @@ _SIGNATURES = {
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
     "thn_attention_prefill_tile_rows": [],
+    "thn_attention_decode_last_variant": [],
     "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -106,11 +107,13 @@ def lib():
 
 _sm_count = {}
 launch_count = 0   # kernels of this library launched (or recorded into a graph) so far
+calls_by_entry: Dict[str, int] = {}    # the same, per entry point of the kernel library
 
 
 def _call(name: str, *args) -> None:
     global launch_count
     launch_count += 1
+    calls_by_entry[name] = calls_by_entry.get(name, 0) + 1
     code = getattr(lib(), name)(*args)
     if code:
         raise KernelError(f"{name}: {lib().thn_last_error().decode()} (status {code})")
@@ -169,11 +172,6 @@ class StepRows:
     n_rows: int
     n_seqs: int
     max_q_len: int           # longest run of rows of one sequence (host knowledge)
-    # Tiles of at most ROW_TILE() consecutive rows of one sequence (first packed row, row count), for
-    # kernels that work on row tiles; None when every sequence brings one row.
-    tile_row0: Optional[torch.Tensor] = None
-    tile_rows: Optional[torch.Tensor] = None
-    n_tiles: int = 0
     # Host knowledge: the most keys a row of this step may see (an upper bound; None: unknown).
     # Kernels may divide their work by it, which changes a result by rounding at most.  A step
     # captured as a graph is replayed only while its bound holds (see context_class).
@@ -311,13 +309,19 @@ STREAM_POLICY = os.environ.get("THN_LINEAR_STREAM", "auto")     # auto | all | n
 _device_counters = {}
 
 
+COUNTER_SLOTS = 1 << 20
+
+
 def _counter_buffer(n: int, device) -> torch.Tensor:
     """Arrival counters for kernels whose last-arriving block finishes a shared result; zero
-    between calls (the kernels reset them)."""
+    between calls (the kernels reset them).  One buffer per device for the life of the
+    process: captured graphs hold its address, so it is never replaced by a larger one."""
+    if n > COUNTER_SLOTS:
+        raise KernelError(f"a kernel asks for {n} arrival counters, the buffer holds {COUNTER_SLOTS}")
     index = torch.device(device).index or 0
     have = _device_counters.get(index)
-    if have is None or have.numel() < n:
-        have = torch.zeros(max(n, 1 << 20), dtype=torch.int32, device=device)   # never regrown in practice: graphs keep its address
+    if have is None:
+        have = torch.zeros(COUNTER_SLOTS, dtype=torch.int32, device=device)
         _device_counters[index] = have
     return have
 
@@ -428,6 +432,32 @@ class KVView:
 
 
 @dataclass
+class RowTiles:
+    """Tiles of at most ``size`` consecutive rows of one sequence, for the prompt attention
+    kernels: first packed row and row count of each tile (int32, on the device).  The
+    kernels start at the end of the list, so it is ordered by the keys a tile sees,
+    fewest first (see :func:`row_tiles_of`)."""
+
+    row0: torch.Tensor
+    rows: torch.Tensor
+    n: int
+    size: int
+
+
+def row_tiles_of(counts, held, size: int):
+    """Host lists (row0, rows) of the tiles of a step whose sequences bring ``counts[i]``
+    rows on top of ``held[i]`` cached tokens, fewest keys first."""
+    tiles, start = [], 0
+    for c, h in zip(counts, held):
+        for r in range(0, c, size):
+            n = min(size, c - r)
+            tiles.append((h + r + n, start + r, n))
+        start += c
+    tiles.sort()
+    return [t[1] for t in tiles], [t[2] for t in tiles]
+
+
+@dataclass
 class RotaryTables:
     cos: torch.Tensor   # float32 [positions, rotary_dim / 2]
     sin: torch.Tensor
@@ -465,28 +495,38 @@ def attention_generic(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, sca
     return out
 
 
+def prompt_attention_tile(dtype: torch.dtype, kv_head_dim: int, page_size: int, n_q: int, n_kv: int) -> int:
+    """Rows per tile that the prompt attention kernel for these sizes works on, or 0 if the
+    sizes go to the kernel that needs no tiles."""
+    if dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv_head_dim, page_size, n_q, n_kv):
+        return lib().thn_attention_prefill_tile_rows()
+    return 0
+
+
 def attention(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float, window: Optional[int],
-              err: torch.Tensor) -> torch.Tensor:
+              err: torch.Tensor, tiles: Optional[RowTiles] = None) -> torch.Tensor:
     """Causal attention of the step's rows over the cache (which already holds the step's
-    own keys).  Chooses the kernel by dtype, head size and step shape."""
+    own keys).  Chooses the kernel by dtype, head size and step shape; the tensor-core
+    kernels for steps of several tokens per sequence need ``tiles``."""
     if q.dtype == torch.bfloat16 and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
         if rows.max_q_len == 1:
             return attention_decode_bf16(q, rows, kv, n_q, scale, window, err)
-        if rows.tile_row0 is not None:
+        if tiles is not None:
             if USE_TCGEN05_ATTENTION and lib().thn_attention_tcgen05_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv):
-                return attention_prefill_tcgen05(q, rows, kv, n_q, scale, window, err)
-            return attention_prefill_bf16(q, rows, kv, n_q, scale, window, err)
+                return attention_prefill_tcgen05(q, rows, tiles, kv, n_q, scale, window, err)
+            return attention_prefill_bf16(q, rows, tiles, kv, n_q, scale, window, err)
     return attention_generic(q, rows, kv, n_q, scale, window, err)
 
 
-def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+def attention_prefill_tcgen05(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                               window: Optional[int], err: torch.Tensor) -> torch.Tensor:
     """tcgen05 / TMEM / TMA flash attention for steps with several tokens per sequence
     (bfloat16, head size 128)."""
     _need(q, "attention q", torch.bfloat16)
     out = torch.empty_like(q)
-    _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(rows.tile_row0), _ptr(rows.tile_rows),
-          rows.n_tiles, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
+    _check_tiles(tiles)
+    _call("thn_attention_prefill_tcgen05", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
+          tiles.n, q.shape[0], _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), kv.storage.shape[0],
           _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale),
           int(window or 0), _ptr(err), _stream())
     return out
@@ -496,17 +536,25 @@ USE_TCGEN05_ATTENTION = os.environ.get("THN_ATTN_TCGEN05", "1").strip().lower() 
 
 
 def ROW_TILE() -> int:
-    """Rows per tile in StepRows.tile_row0 / tile_rows (what the prompt attention kernel works on)."""
+    """Rows per tile that the tensor-core prompt attention kernels work on."""
     return lib().thn_attention_prefill_tile_rows()
 
 
-def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
+def _check_tiles(tiles: RowTiles) -> None:
+    if tiles.size != ROW_TILE():
+        raise KernelError(f"prompt attention: row tiles of {tiles.size} rows, the kernel works on {ROW_TILE()}")
+    _need(tiles.row0, "row tiles", torch.int32)
+    _need(tiles.rows, "row tiles", torch.int32)
+
+
+def attention_prefill_bf16(q: torch.Tensor, rows: StepRows, tiles: RowTiles, kv: KVView, n_q: int, scale: float,
                            window: Optional[int], err: torch.Tensor) -> torch.Tensor:
     """Tensor-core flash attention for steps with several tokens per sequence."""
     _need(q, "attention q", torch.bfloat16)
     out = torch.empty_like(q)
-    _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(rows.tile_row0), _ptr(rows.tile_rows),
-          rows.n_tiles, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
+    _check_tiles(tiles)
+    _call("thn_attention_prefill_bf16", _ptr(out), _ptr(q), _ptr(tiles.row0), _ptr(tiles.rows),
+          tiles.n, _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_q, float(scale), int(window or 0),
           _ptr(err), _stream())
     return out
@@ -564,7 +612,8 @@ FUSE_DECODE_ATTENTION = os.environ.get("THN_FUSE_DECODE", "1").strip().lower() n
 
 def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
                   rotary: Optional[RotaryTables], rows: StepRows, kv: KVView, n_q: int, scale: float,
-                  window: Optional[int], write_cache: bool, err: torch.Tensor) -> torch.Tensor:
+                  window: Optional[int], write_cache: bool, err: torch.Tensor,
+                  tiles: Optional[RowTiles] = None) -> torch.Tensor:
     """From the raw q/k/v rows of a step to the attention output: per-head q/k norm, rotation,
     cache write and attention over the cache.  One kernel for single-token steps in bfloat16
     with head norm and full rotation at the tensor-core kernel's sizes; otherwise
@@ -575,7 +624,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
                and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv))
     if not fusable:
         q = qk_norm_rope_cache(qkv, q_gain, k_gain, eps, rotary, rows, kv, n_q, write_cache, err)
-        return attention(q, rows, kv, n_q, scale, window, err)
+        return attention(q, rows, kv, n_q, scale, window, err, tiles)
     n_seqs = rows.n_rows
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
     if tuple(qkv.shape) != (n_seqs, width):
@@ -634,7 +683,7 @@ def gather_i32(src: torch.Tensor, index: torch.Tensor, out: Optional[torch.Tenso
 
 
 __all__ = [
-    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "StepRows", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
+    "KernelError", "KernelLibraryError", "KVView", "RotaryTables", "RowTiles", "StepRows", "row_tiles_of", "prompt_attention_tile", "linear_stream", "linear_swiglu", "linear_tcgen05", "add_rmsnorm", "advance",
     "ROW_TILE", "attention", "attention_decode_bf16", "attention_generic", "attention_prefill_bf16", "attention_prefill_tcgen05", "decode_splits", "choose_tokens", "gather_i32", "gather_rows", "lib", "linear", "new_error_word",
     "qk_norm_rope_cache", "qkv_attention", "raise_on_device_error", "rmsnorm", "rope_table", "scatter_i32", "step_rows", "swiglu",
 ]

@@ -14,7 +14,7 @@ makes the mixer read the cache another entry wrote: it computes only its queries
 
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -23,7 +23,7 @@ from ..cache.sequence_cache import CacheNeed, KVSpec
 from ..config.base import PartSpec, ScheduleEntry
 from ..weights.loader import GAIN, MATRIX, TensorSpec
 from .registry import part_class, register_part
-from .runtime import Runtime, StepContext
+from .runtime import HostBatch, Runtime, StepContext
 
 
 @register_part("mixer", "attention")
@@ -53,6 +53,7 @@ class Attention:
         self.w_o = runtime.tensor(spec, "o_proj")
         self.q_gain = runtime.tensor(spec, "q_norm") if self.eps is not None else None
         self.k_gain = runtime.tensor(spec, "k_norm") if self.eps is not None else None
+        self.dtype = runtime.dtype
         self.position = None
         position_spec = p.get("position")
         if position_spec is not None:
@@ -64,10 +65,28 @@ class Attention:
     def cache_need(self) -> CacheNeed:
         return KVSpec(self.n_kv, self.head_dim, self.window)
 
+    def _tile(self, page_size: int) -> int:
+        return ops.prompt_attention_tile(self.dtype, self.head_dim, page_size, self.n_q, self.n_kv)
+
+    def step_inputs(self, batch: HostBatch, out: Dict[str, List[int]]) -> None:
+        """The prompt attention kernels work on tiles of consecutive rows of one sequence; the
+        host knows every length, so it lists them (every attention of a model that wants
+        tiles of one size shares one list)."""
+        size = self._tile(batch.page_size) if batch.max_count > 1 else 0
+        if size and f"row_tiles/{size}/row0" not in out:
+            out[f"row_tiles/{size}/row0"], out[f"row_tiles/{size}/rows"] = ops.row_tiles_of(
+                batch.counts, batch.held, size)
+
     def forward(self, x: torch.Tensor, ctx: StepContext, entry: ScheduleEntry) -> torch.Tensor:
         kv = ctx.cache.kv_view(entry.cache)
+        tiles = None
+        if ctx.rows.max_q_len > 1:
+            size = self._tile(kv.page_size)
+            row0 = ctx.inputs.get(f"row_tiles/{size}/row0") if size else None
+            if row0 is not None:
+                tiles = ops.RowTiles(row0, ctx.inputs[f"row_tiles/{size}/rows"], row0.shape[0], size)
         qkv = ops.linear(x, self.w_qkv, err=ctx.err)
         a = ops.qkv_attention(qkv, self.q_gain, self.k_gain, self.eps if self.eps is not None else 1.0,
                               self.position.tables() if self.position is not None else None,
-                              ctx.rows, kv, self.n_q, self.scale, self.window, entry.writes_cache, ctx.err)
+                              ctx.rows, kv, self.n_q, self.scale, self.window, entry.writes_cache, ctx.err, tiles)
         return ops.linear(a, self.w_o, err=ctx.err)

@@ -33,8 +33,9 @@ class Embedding:
 class LMHead:
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> List[TensorSpec]:
+        copies = (spec.tensors["stored_copy"],) if "stored_copy" in spec.tensors else ()
         return [TensorSpec(spec.tensors["weight"], (int(spec.params["vocab_size"]), int(spec.params["hidden_size"])),
-                           MATRIX)]
+                           MATRIX, copies=copies)]
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         self.weight = runtime.tensor(spec, "weight")

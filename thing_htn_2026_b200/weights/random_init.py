@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, Iterable
+from typing import Callable, Dict, Iterable
 
 import torch
 
@@ -28,16 +28,44 @@ def _tensor_seed(seed: int, index: int) -> int:
     return (int(seed) * 1_000_003 + index * 7919 + 12345) % (2 ** 63 - 1)
 
 
+def _normal(t, generator, matrix_std, gain_std):
+    return t.normal_(0.0, matrix_std, generator=generator)
+
+
+def _one_plus_normal(t, generator, matrix_std, gain_std):
+    return t.normal_(0.0, gain_std, generator=generator).add_(1.0)
+
+
+def _zeros(t, generator, matrix_std, gain_std):
+    return t.zero_()
+
+
+# How a tensor is drawn, by the name in ``TensorSpec.init``.  ``fill(t, generator, matrix_std,
+# gain_std)`` fills ``t`` (float32 on the CPU, the held dtype on a device) in place.
+INITIALIZERS: Dict[str, Callable] = {"normal": _normal, "one_plus_normal": _one_plus_normal, "zeros": _zeros}
+# The rule of a spec that names none, by its role.
+ROLE_INIT = {MATRIX: "normal", GAIN: "one_plus_normal", TABLE: "zeros"}
+
+
+def register_initializer(name: str, fill: Callable) -> None:
+    """A new drawing rule (a gain stored as ``w`` of ``1 + w``, a bias, ...) for specs that
+    name it in ``TensorSpec.init``."""
+    if name in INITIALIZERS and INITIALIZERS[name] is not fill:
+        raise ValueError(f"initializer '{name}' is already registered")
+    INITIALIZERS[name] = fill
+
+
 def _draw(spec: TensorSpec, generator: torch.Generator, device, matrix_std: float, gain_std: float,
           dtype: torch.dtype) -> torch.Tensor:
+    rule = spec.init or ROLE_INIT.get(spec.role)
+    if rule not in INITIALIZERS:
+        raise KeyError(f"{spec.name}: no initializer named '{rule}' (role '{spec.role}'); known: "
+                       + ", ".join(sorted(INITIALIZERS)))
     if spec.role == TABLE:
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        return INITIALIZERS[rule](torch.zeros(spec.shape, dtype=torch.int32, device=device), generator,
+                                  matrix_std, gain_std)
     t = torch.empty(spec.shape, dtype=torch.float32 if device == "cpu" else dtype, device=device)
-    if spec.role == GAIN:
-        t.normal_(0.0, gain_std, generator=generator).add_(1.0)
-    else:
-        t.normal_(0.0, matrix_std, generator=generator)
-    return t.to(dtype)
+    return INITIALIZERS[rule](t, generator, matrix_std, gain_std).to(dtype)
 
 
 def specs_of(config: ModelConfig) -> Dict[str, TensorSpec]:
@@ -55,15 +83,23 @@ def random_tensors_cpu(config: ModelConfig, seed: int, dtype: torch.dtype = torc
 
 
 def write_random_model(model_dir: str, config: ModelConfig, seed: int, dtype: torch.dtype = torch.float32,
-                       matrix_std: float = 0.02, gain_std: float = 0.1) -> str:
-    """Write config.json and model.safetensors; returns the folder."""
+                       matrix_std: float = 0.02, gain_std: float = 0.1, device="cpu") -> str:
+    """Write config.json and model.safetensors; returns the folder.  ``device``: where the
+    values are drawn (a GPU draws a large model in seconds; its generator gives other values
+    than the CPU's for the same seed)."""
     os.makedirs(model_dir, exist_ok=True)
     data = config.to_dict()
     data["torch_dtype"] = {torch.float32: "float32", torch.bfloat16: "bfloat16",
                            torch.float16: "float16"}[dtype]
     with open(os.path.join(model_dir, "config.json"), "w") as handle:
         json.dump(data, handle, indent=1)
-    tensors = random_tensors_cpu(config, seed, dtype, matrix_std, gain_std)
+    if str(device) == "cpu":
+        tensors = random_tensors_cpu(config, seed, dtype, matrix_std, gain_std)
+    else:
+        from ..models.decoder import tensor_specs_of_plan
+        drawn = random_tensors_on_device(tensor_specs_of_plan(config.plan()), seed, dtype, torch.device(device),
+                                         matrix_std, gain_std)
+        tensors = {name: t.to(dtype).cpu() for name, t in drawn.items()}
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": str(seed)})
     return model_dir
