@@ -181,10 +181,12 @@ def run_ours(args):
             handles = []
             for _ in range(steps):
                 handles.append(backend.launch_decode(slots))
-                if len(handles) > 4:
+                if len(handles) > 3:
                     backend.fetch(handles.pop(0))
             end.record()
             torch.cuda.synchronize()
+            for handle in handles:
+                backend.fetch(handle)
             if args.profiler_range == "decode" and sample_clocks:
                 torch.cuda.profiler.stop()
             clocks = sampler.stop() if sampler else None

@@ -16,6 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def run_bench(*args):
     result = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True,
                             timeout=600, cwd=ROOT)
+    if result.returncode not in (0, 2):
+        print(result.stderr[-3000:])           # shown by pytest when the test fails
     return result.returncode, result.stdout.strip().splitlines()
 
 

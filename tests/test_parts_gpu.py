@@ -143,12 +143,17 @@ def test_attention_part_and_block(dtype, n_q, n_kv, D, window):
                                         "scale": D ** -0.5, "window": window, "qk_norm_eps": eps, "position": position},
                           names)
     rt = runtime(dtype, tensors)
-    mixer = part_class("mixer", "attention")(mixer_spec, rt)
-    ffn = part_class("ffn", "swiglu")(PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter},
-                                               {"gate_proj": "g", "up_proj": "u", "down_proj": "d"}), rt)
-    norm1 = part_class("norm", "rmsnorm")(PartSpec("rmsnorm", {"size": hidden, "eps": eps}, {"weight": "n1"}), rt)
-    norm2 = part_class("norm", "rmsnorm")(PartSpec("rmsnorm", {"size": hidden, "eps": eps}, {"weight": "n2"}), rt)
-    block = part_class("block", "pre_norm")(mixer, ffn, norm1, norm2)
+    # the block builds its own members from the specs among its parameters
+    block = part_class("block", "pre_norm")(PartSpec("pre_norm", {
+        "mixer": mixer_spec,
+        "ffn": PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter},
+                        {"gate_proj": "g", "up_proj": "u", "down_proj": "d"}),
+        "norm_mixer": PartSpec("rmsnorm", {"size": hidden, "eps": eps}, {"weight": "n1"}),
+        "norm_ffn": PartSpec("rmsnorm", {"size": hidden, "eps": eps}, {"weight": "n2"}),
+    }), rt)
+    mixer = block.mixer
+    assert block.cache_need() == mixer.cache_need()
+    assert {s.name for s in type(block).tensor_specs(PartSpec("pre_norm", {"mixer": mixer_spec}))} == set(names.values())
     for part in rt.shared.values():
         part.ensure(512)
 

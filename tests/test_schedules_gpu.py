@@ -301,12 +301,28 @@ def test_unmapped_page_sets_its_bit(kernel):
     o = ops()
     bits = error_case(kernel, "page")
     assert bits & o.ERR_PAGE_UNMAPPED, f"error word {bits}"
-    if kernel == "tcgen05":
-        # The block whose loader stopped at the missing page leaves its other warps waiting for
-        # that page; their bounded waits run out, they say so, and the kernel ends.
-        assert bits & o.ERR_WAIT_TIMEOUT
-    else:
-        assert bits == o.ERR_PAGE_UNMAPPED
+    assert bits == o.ERR_PAGE_UNMAPPED
+
+
+def test_a_wait_that_runs_out_sets_its_bit_and_the_kernel_returns():
+    """The tcgen05 prompt attention with its loader told (by a switch that exists for this
+    test) to bring no key or value page: the waits for them are bounded by a clock, run out
+    after 20 ms, set their bit, and every block leaves through its common exit.  The next
+    launch, with the switch off, is right again."""
+    o = ops()
+    assert o.lib().thn_attention_tcgen05_test_skip_loads(1) == 0
+    try:
+        fix = kernels.PagedFixture(2, 128, [70], torch.bfloat16)
+        rows, cu = fix.rows([70])
+        q = kernels.rand((70, 4 * 128), torch.bfloat16, 1).to(DEV)
+        err = o.new_error_word(DEV)
+        o.attention_prefill_tcgen05(q, rows, rows.tiles, fix.kv, 4, 128 ** -0.5, None, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == o.ERR_WAIT_TIMEOUT
+    finally:
+        assert o.lib().thn_attention_tcgen05_test_skip_loads(0) == 0
+    got, want = kernels.attention_case("tcgen05", torch.bfloat16, 4, 2, 128, [70, 131], [70, 131], None)
+    kernels.close(got, want, torch.bfloat16, "tcgen05 attention after a timed-out launch")
 
 
 @pytest.mark.parametrize("kernel", ["rope", "fused"])

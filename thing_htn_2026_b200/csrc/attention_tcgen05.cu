@@ -173,6 +173,11 @@ __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const float (&r)[3
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// For the test of the bounded waits only: when set, the loader brings Q and then no key or value
+// page at all, so that the waits for them run out, say so in the error word, and the block leaves
+// through its common exit.
+__device__ int g_test_skip_kv_loads = 0;
+
 // map_q: q as [rows, n_q * 128], boxes of 64 x 128 rows.  map_kv: the cache entry as
 // [pages * 2 * n_kv * 64, 128], boxes of 64 x 64 rows (one half of one head's page).
 __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
@@ -239,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         // K pages and V pages have rings of their own: a K page is free again once S = Q K^T has
         // read it, long before the tile's V page, so K runs one tile further ahead: K(0), K(1),
         // V(0), K(2), V(1), ...
-        const int n_it = t_last - t_first + 1;
+        const int n_it = g_test_skip_kv_loads ? 0 : t_last - t_first + 1;
         auto load = [&](int it, int which) {        // which: 0 = K, 1 = V
             const int s = it % kStages;
             uint64_t* empty = which ? v_empty : k_empty;
@@ -480,6 +485,18 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 }  // namespace
 
 // 1 if thn_attention_prefill_tcgen05 takes this shape.
+// Test switch (see g_test_skip_kv_loads): nonzero makes every later launch on the current device
+// run into its wait limit.  Returns a status.
+THN_API int thn_attention_tcgen05_test_skip_loads(int on) {
+    const int value = on ? 1 : 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_test_skip_kv_loads, &value, sizeof(int));
+    if (e != cudaSuccess) {
+        thn_set_error("attention_tcgen05 test switch: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return THN_OK;
+}
+
 THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q, int n_kv) {
     return head_dim == D && page_size == kKeys && n_kv > 0 && n_q % n_kv == 0;
 }

@@ -96,7 +96,8 @@ class DeviceBackend:
 
     def close_batch(self, slots: Sequence[int]) -> None:
         self.cache.close(slots)
-        ops.raise_on_device_error(self.err, "generation")
+        ops.raise_on_device_error(self.err, "generation")      # reads the error word: every step has ended
+        self._ring_busy = [False] * len(self._ring)            # handles of an abandoned batch are void
 
     # ------------------------------------------------------------------ steps
 

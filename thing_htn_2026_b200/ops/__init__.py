@@ -71,6 +71,7 @@ _SIGNATURES = {
     "thn_attention_prefill_tile_rows": [],
     "thn_attention_decode_last_variant": [],
     "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
+    "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                       c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                       c_int, c_void_p, c_void_p],
