@@ -500,12 +500,17 @@ def time_reference(args, ref, torch, cfg, n_layers, full_layers, warmup):
     # time to the first token of one 2,048-token prompt
     list(ref.generate(prompts(1, PREFILL_TOKENS), 2))
     times = []
-    for _ in range(3):
+    for rep in range(3):
         ids = prompts(1, PREFILL_TOKENS)
         torch.cuda.synchronize()
+        if args.profiler_range == "prefill" and rep == 2:
+            torch.cuda.profiler.start()
         t0 = time.perf_counter()
         for tokens in ref.generate(ids, 1):
             times.append(1e3 * (time.perf_counter() - t0))
+        if args.profiler_range == "prefill" and rep == 2:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
     prefill_ms = statistics.median(times)
     flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
 

@@ -192,3 +192,30 @@ def test_greedy_across_classes_of_context_length(tiny_models, monkeypatch):
         check_greedy(tiny_models[name], "bfloat16", prompt, emitted)
     assert {(2, 0), (2, 1), (1, 1), (1, 2)} <= set(engine.backend.graphs), sorted(engine.backend.graphs)
     engine.backend.cache.check()
+
+
+def test_windowed_group_gives_pages_back_while_it_generates(tiny_models):
+    """Generation maps pages step by step, so a layer group with a window of 70 keys holds a
+    few pages per sequence however long the sequence grows, while the group that keeps all
+    keys holds them all; the tokens are the plain argmax throughout."""
+    name = "d"
+    prompts = [tiny.tokens(name, n, 950 + i) for i, n in enumerate([10, 90])]
+    engine = engine_for(tiny_models[name], "float32")
+    book = None
+    emitted = [[], []]
+    most_windowed = 0
+    for n, step in enumerate(engine.generate(prompts, 400)):
+        book = engine.backend.cache.book
+        windowed = [g for g, group in enumerate(book.groups) if group.window is not None]
+        full = [g for g, group in enumerate(book.groups) if group.window is None]
+        assert len(windowed) == 1 and len(full) == 1
+        most_windowed = max(most_windowed, book.pages[windowed[0]].n_held)
+        for seq, token in zip(emitted, step):
+            seq.append(token)
+    # 70 keys span at most three pages of 64, plus the page being written; two sequences, and the
+    # backend's scratch slot holds one page
+    assert most_windowed <= 2 * 4 + 1, most_windowed
+    assert book.pages[full[0]].n_held == 1, "the batch has ended: only the scratch page is held"
+    for prompt, tokens in zip(prompts, emitted):
+        check_greedy(tiny_models[name], "float32", prompt, tokens)
+    engine.backend.cache.check()

@@ -48,23 +48,50 @@ def test_decode_attention_with_many_pairs(n_seqs, splits):
     got, want = kernels.attention_case("decode" + splits, dtype, 32, 8, 128, lengths, [1] * n_seqs, None)
     kernels.close(got, want, dtype, f"decode attention, {n_seqs} sequences, splits {splits or 'auto'}")
     variant = o.lib().thn_attention_decode_last_variant()
-    assert variant % 10 == 0, "hundreds of pairs were given to clusters"
-    seen_variants[(n_seqs, splits)] = variant // 10
+    assert variant % 10 == 2, "hundreds of pairs, one split: the streaming kernel's step"
+
+
+@pytest.mark.parametrize("stages", [3, 6])
+@pytest.mark.parametrize("n_seqs", [40, 48, 56, 64])
+def test_decode_attention_with_many_pairs_one_block_per_pair(n_seqs, stages):
+    """The same steps with the streaming kernel switched off (one block per pair with six,
+    three or two tile buffers, at the top a second pass) and with its deeper ring of tile
+    buffers."""
+    o = ops()
+    dtype = torch.bfloat16
+    lengths = spread_lengths(n_seqs)
+    try:
+        o.lib().thn_set_decode_stream(0 if stages == 3 else 1, stages)
+        got, want = kernels.attention_case("decode", dtype, 32, 8, 128, lengths, [1] * n_seqs, None)
+        variant = o.lib().thn_attention_decode_last_variant()
+    finally:
+        o.lib().thn_set_decode_stream(1, 3)
+    kernels.close(got, want, dtype, f"decode attention, {n_seqs} sequences")
+    if stages == 3:
+        assert variant % 10 == 0, "hundreds of pairs were given to clusters"
+        seen_variants[n_seqs] = variant // 10
+    else:
+        assert variant == 62
 
 
 def test_decode_attention_many_pairs_took_every_branch():
-    """The four batch sizes above reach the launcher's variants with two and three tile
+    """The four batch sizes above reach the one-block-per-pair variants with two and three tile
     buffers (which of them at which size depends on the blocks an SM holds)."""
-    if len(seen_variants) < 8:
-        pytest.skip("runs after test_decode_attention_with_many_pairs")
-    buffers = {v for (n, s), v in seen_variants.items() if s == ""}
-    assert {2, 3} <= buffers, f"tile buffers seen: {sorted(seen_variants.items())}"
+    if len(seen_variants) < 4:
+        pytest.skip("runs after test_decode_attention_with_many_pairs_one_block_per_pair")
+    assert {2, 3} <= set(seen_variants.values()), f"tile buffers seen: {sorted(seen_variants.items())}"
 
 
 @pytest.mark.parametrize("n_seqs", [40, 64])
 def test_fused_decode_attention_with_many_pairs(n_seqs):
     kernels.fused_decode_case(32, 8, 128, None, torch.float32, spread_lengths(n_seqs))
-    assert ops().lib().thn_attention_decode_last_variant() % 10 == 0
+    assert ops().lib().thn_attention_decode_last_variant() % 10 == 2
+    try:
+        ops().lib().thn_set_decode_stream(0, 3)
+        kernels.fused_decode_case(32, 8, 128, None, torch.float32, spread_lengths(n_seqs))
+        assert ops().lib().thn_attention_decode_last_variant() % 10 == 0
+    finally:
+        ops().lib().thn_set_decode_stream(1, 3)
 
 
 def test_decode_attention_few_pairs_meets_in_a_cluster():

@@ -9,6 +9,7 @@
 // head is 64 * head_dim contiguous values.  Tiles reach shared memory with 16-byte
 // cp.async copies; rows are padded by 16 bytes so that ldmatrix reads do not collide.
 // Instantiated for head sizes 64 and 128; other sizes use the generic kernel.
+#include <cuda.h>
 #include <math.h>
 
 #include <algorithm>
@@ -742,6 +743,481 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     }
 }
 
+// ------------------------------------------------------------------ single tokens, many sequences
+//
+// When a step brings more (sequence, kv head) pairs than the GPU holds clusters, the key range
+// of a pair is not split and the kernel below takes over.  It is built for bandwidth: a fixed
+// number of blocks, as many as are resident at once, each of which works through several
+// pairs, one after the other, without letting its loads run dry in between.
+//
+//   * Warp 4 is the loader.  It walks the block's pairs and their pages (32 page numbers per
+//     lookup, the next pair's position and slot requested a pair ahead) and one lane fetches
+//     every K tile and V tile with `cp.async.bulk.tensor` from a tensor map over the cache
+//     entry ([pages * 2 * n_kv * 64 rows, head_dim], boxes of 64 values x 64 rows, 128-byte
+//     swizzle, so that ldmatrix reads no bank twice without padded rows) onto the tile
+//     buffer's mbarrier.  It runs up to STAGES tiles ahead of the arithmetic, across pair
+//     boundaries.
+//   * Warp 5 prepares the queries of the NEXT pair while the arithmetic works on this one: it
+//     copies the pair's query heads into shared memory, or (FUSED) normalises and rotates
+//     them from the step's raw q/k/v rows, and normalises and rotates the step's own key,
+//     writes it and the value to the cache and leaves both in shared memory for the tile.
+//   * Warps 0-3 are the arithmetic of attention_decode_kernel (16 keys of every tile each,
+//     the same fragments, masks and rounding), reading the swizzled tiles.  They give a tile
+//     buffer back with one arrival per warp on its second mbarrier and meet among
+//     themselves on a named barrier only where a pair ends (the merge of their four partial
+//     results, in scratch of its own, as the tile buffers are in use).
+//
+// Every wait on an mbarrier is bounded by the clock (20 ms); a waiter that gives up sets
+// THN_ERR_WAIT_TIMEOUT, tells the others, and the loader waits (bounded again) for the
+// copies it still has in flight before it returns.
+
+constexpr int kStreamThreads = 192;            // four arithmetic warps, the loader, the preparer
+constexpr unsigned long long kStreamWaitNs = 20ull * 1000 * 1000;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long start = 0;
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (start == 0) start = now;
+        else if (now - start > kStreamWaitNs) return false;
+    }
+}
+__device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// the four arithmetic warps among themselves (barrier 0 is __syncthreads)
+__device__ __forceinline__ void sync_arithmetic() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Byte offset of the 16 bytes that hold values [d, d + 8) of row `row` in a tile that came as
+// boxes of 64 values x 64 rows with the 128-byte swizzle: a row of a box is 128 bytes, its eight
+// 16-byte pieces are exchanged by the row's low three bits, the second box follows the first.
+__device__ __forceinline__ uint32_t swizzled(int row, int d) {
+    return (uint32_t)((d >> 6) * (kTile * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4));
+}
+
+// qk_tile and pv_tile on swizzled tiles.
+template <int D, int NK>
+__device__ __forceinline__ void qk_tile_swizzled(float (&s)[NK][4], const uint32_t (&qf)[D / 16][4],
+                                                 const unsigned char* k_tile, int key_block0, int lane) {
+#pragma unroll
+    for (int n = 0; n < NK; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NK; n += 2) {
+            uint32_t b[4];
+            const int key = (key_block0 + n + (lane >> 4)) * 8 + (lane & 7);
+            ldmatrix_x4(b, k_tile + swizzled(key, kk * 16 + ((lane >> 3) & 1) * 8));
+            mma_bf16(s[n], qf[kk], b[0], b[1]);
+            mma_bf16(s[n + 1], qf[kk], b[2], b[3]);
+        }
+    }
+}
+template <int D, int NK>
+__device__ __forceinline__ void pv_tile_swizzled(float (&o)[D / 8][4], const uint32_t (&pf)[NK / 2][4],
+                                                 const unsigned char* v_tile, int key_block0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NK / 2; ++kk) {
+#pragma unroll
+        for (int nd = 0; nd < D / 8; nd += 2) {
+            uint32_t b[4];
+            const int key = (key_block0 + 2 * kk) * 8 + ((lane >> 3) & 1) * 8 + (lane & 7);
+            ldmatrix_x4_trans(b, v_tile + swizzled(key, (nd + (lane >> 4)) * 8));
+            mma_bf16(o[nd], pf[kk], b[0], b[1]);
+            mma_bf16(o[nd + 1], pf[kk], b[2], b[3]);
+        }
+    }
+}
+
+// Shared memory of the streaming kernel for groups of G query heads: tile buffers (each K tile
+// and V tile 64 * D * 2 bytes; the buffers start the block's shared memory, 1024-byte aligned
+// for the swizzle), q [16][D], the step's own key and value for two pairs [2][2][D], the merge
+// scratch ((max, sum) of four warps, their outputs [4][G][D + 8], weights), flags and barriers.
+template <int D>
+constexpr size_t stream_smem(int stages, int G) {
+    return (size_t)stages * 2 * kTile * D * 2 + 16 * D * 2 + 4 * D * 2 + (size_t)(128 + 4 * G * (D + 8) + 64 + 32) * 4 +
+           (size_t)(2 * stages + 2) * 8 + 16;
+}
+
+template <int D, int STAGES, bool FUSED>
+__global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_decode_stream_kernel(
+    const __grid_constant__ CUtensorMap map_kv, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
+    const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_seqs, int n_q,
+    float scale_log2, int window, int* __restrict__ err, FusedInput fused) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int kOPitch = D + 8;
+    constexpr int E = D / 64, kHalf = D / 2;
+    constexpr uint32_t kTileBytes = kTile * D * 2;
+    extern __shared__ __align__(1024) unsigned char tiles[];
+    __nv_bfloat16* q_smem = reinterpret_cast<__nv_bfloat16*>(tiles + (size_t)STAGES * 2 * kTileBytes);   // [16][D]
+    __nv_bfloat16* own_smem = q_smem + 16 * D;                          // [2 pairs][key, value][D]
+    const int G = n_q / kv.n_kv;
+    float* m_smem = reinterpret_cast<float*>(own_smem + 4 * D);         // [4][16]
+    float* l_smem = m_smem + 64;                                        // [4][16]
+    float* o_smem = l_smem + 64;                                        // [4][G][kOPitch]
+    float* wgt_smem = o_smem + 4 * G * kOPitch;                         // [16][4]
+    float* ml_smem = wgt_smem + 64;                                     // [16][2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(ml_smem + 32);         // [STAGES] a tile pair has landed
+    uint64_t* empty = full + STAGES;                                    // [STAGES] the four warps are done with it
+    uint64_t* q_full = empty + STAGES;                                  // the next pair's q (and own key, value) are ready
+    uint64_t* q_empty = q_full + 1;                                     // the four warps hold q in registers
+    volatile int* give_up = reinterpret_cast<volatile int*>(q_empty + 1);
+    volatile int* position_bad = give_up + 1;                           // [2] by pair parity
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_pairs = n_seqs * kv.n_kv;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 4);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(q_empty, 4);
+        *give_up = (smem_u32(tiles) & 1023u) ? 1 : 0;      // the swizzle's arithmetic needs the alignment
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (*give_up) {
+        if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+        return;
+    }
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- the loader
+        int it = 0;                                        // tiles requested so far by this block
+        bool ok = true;
+        int pair = blockIdx.x;
+        int pos_next = 0, slot_next = 0;
+        if (pair < n_pairs) {
+            pos_next = row_pos[pair / kv.n_kv];
+            slot_next = row_slot[pair / kv.n_kv];
+        }
+        for (; pair < n_pairs && ok && !*give_up; pair += gridDim.x) {
+            const int kvh = pair % kv.n_kv;
+            const int pos = pos_next, slot = slot_next;
+            const int after = pair + gridDim.x;
+            if (after < n_pairs) {                          // a pair ahead: on its way while this pair's tiles are requested
+                pos_next = row_pos[after / kv.n_kv];
+                slot_next = row_slot[after / kv.n_kv];
+            }
+            int first_key = 0;
+            if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
+            const int t_first = first_key / kTile, t_last = pos / kTile;
+            const int* pages = kv.block_table + (size_t)slot * kv.bt_stride;
+            for (int t0 = t_first; t0 <= t_last && ok; t0 += 32) {
+                const int mine = t0 + lane <= t_last ? pages[t0 + lane] : 0;
+                const int n = min(32, t_last - t0 + 1);
+                for (int j = 0; j < n && ok; ++j, ++it) {
+                    const int page = __shfl_sync(0xffffffffu, mine, j);
+                    const int s = it % STAGES;
+                    if (lane == 0) {
+                        ok = mbar_wait(empty + s, ((it / STAGES) & 1) ^ 1);
+                        if (!ok) {
+                            if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                        } else if (page < 0) {
+                            if (err) atomicOr(err, THN_ERR_PAGE_UNMAPPED);
+                            mbar_arrive(full + s);          // nothing is fetched; the arithmetic goes on over what lies there
+                        } else {
+                            unsigned char* dst = tiles + (size_t)s * 2 * kTileBytes;
+                            mbar_expect_tx(full + s, 2 * kTileBytes);
+                            const int k_row = ((page * 2 + 0) * kv.n_kv + kvh) * kTile;
+                            const int v_row = ((page * 2 + 1) * kv.n_kv + kvh) * kTile;
+#pragma unroll
+                            for (int half = 0; half < D / 64; ++half) {
+                                tma_tile(dst + half * (kTile * 128), &map_kv, full + s, half * 64, k_row);
+                                tma_tile(dst + kTileBytes + half * (kTile * 128), &map_kv, full + s, half * 64, v_row);
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                }
+            }
+        }
+        if (!ok) *give_up = 1;
+        // Copies still in flight must land before the block's shared memory is given up: wait
+        // for the last STAGES tiles requested (a tile the arithmetic has taken is complete).
+        if (lane == 0) {
+            for (int back = 1; back <= STAGES && back <= it; ++back) {
+                const int j = it - back;
+                mbar_wait(full + j % STAGES, (j / STAGES) & 1);
+            }
+        }
+        return;
+    }
+
+    if (warp == 5) {
+        // ---------------------------------------------------------------- the preparer
+        const int d0 = lane * E;
+        for (int c = lane; c < 16 * (D / 8); c += 32)                   // rows beyond the group stay zero
+            *reinterpret_cast<uint4*>(q_smem + c * 8) = make_uint4(0, 0, 0, 0);
+        float qg_lo[E], qg_hi[E], kg_lo[E], kg_hi[E];
+        if (FUSED) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                qg_lo[e] = gain_at(fused.q_gain, fused.gain_f32, d0 + e);
+                qg_hi[e] = gain_at(fused.q_gain, fused.gain_f32, kHalf + d0 + e);
+                kg_lo[e] = gain_at(fused.k_gain, fused.gain_f32, d0 + e);
+                kg_hi[e] = gain_at(fused.k_gain, fused.gain_f32, kHalf + d0 + e);
+            }
+        }
+        __syncwarp();
+        bool ok = true;
+        int k = 0;
+        for (int pair = blockIdx.x; pair < n_pairs && ok && !*give_up; pair += gridDim.x, ++k) {
+            const int b = pair / kv.n_kv, kvh = pair % kv.n_kv;
+            // what the pair needs from global memory is requested before the wait for q's buffer
+            __nv_bfloat16 raw_lo[4][E], raw_hi[4][E];                     // up to four heads in flight
+            const int pos = FUSED ? row_pos[b] : 0;
+            const bool position_ok = !FUSED || pos < fused.table_len;
+            if (lane == 0) ok = mbar_wait(q_empty, (k & 1) ^ 1);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (!ok) {
+                if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+                break;
+            }
+            if (!FUSED) {
+                for (int c = lane; c < G * (D / 8); c += 32)
+                    *reinterpret_cast<uint4*>(q_smem + c * 8) =
+                        *reinterpret_cast<const uint4*>(q + ((size_t)b * n_q + kvh * G) * D + c * 8);
+            } else {
+                const int at = position_ok ? pos : 0;
+                float c[E], sn[E];
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    c[e] = rnd<__nv_bfloat16>(fused.cos_tab[(size_t)at * kHalf + d0 + e]);
+                    sn[e] = rnd<__nv_bfloat16>(fused.sin_tab[(size_t)at * kHalf + d0 + e]);
+                }
+                const __nv_bfloat16* qkv_row = fused.qkv + (size_t)b * (n_q + 2 * kv.n_kv) * D;
+                for (int r0 = 0; r0 < G; r0 += 4) {                     // four heads' loads in flight at a time
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = min(r0 + i, G - 1);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) {
+                            raw_lo[i][e] = qkv_row[(size_t)(kvh * G + r) * D + d0 + e];
+                            raw_hi[i][e] = qkv_row[(size_t)(kvh * G + r) * D + kHalf + d0 + e];
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (r0 + i >= G) break;
+                        __nv_bfloat16 lo[E], hi[E];
+                        norm_rotate_head<D>(raw_lo[i], raw_hi[i], qg_lo, qg_hi, fused.eps, c, sn, lo, hi);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) {
+                            q_smem[(r0 + i) * D + d0 + e] = lo[e];
+                            q_smem[(r0 + i) * D + kHalf + d0 + e] = hi[e];
+                        }
+                    }
+                }
+                if (fused.write_cache) {
+                    // the step's own key (normalised, rotated) and value: into the cache now, and
+                    // kept for the last tile, which may have been fetched without them
+                    const __nv_bfloat16* k_row = qkv_row + (size_t)(n_q + kvh) * D;
+                    const __nv_bfloat16* v_row = qkv_row + (size_t)(n_q + kv.n_kv + kvh) * D;
+                    __nv_bfloat16 raw_k_lo[E], raw_k_hi[E], new_k_lo[E], new_k_hi[E], new_v_lo[E], new_v_hi[E];
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        raw_k_lo[e] = k_row[d0 + e];
+                        raw_k_hi[e] = k_row[kHalf + d0 + e];
+                        new_v_lo[e] = v_row[d0 + e];
+                        new_v_hi[e] = v_row[kHalf + d0 + e];
+                    }
+                    const int page = position_ok ? (kv.block_table + (size_t)row_slot[b] * kv.bt_stride)[pos / kTile] : -1;
+                    norm_rotate_head<D>(raw_k_lo, raw_k_hi, kg_lo, kg_hi, fused.eps, c, sn, new_k_lo, new_k_hi);
+                    __nv_bfloat16* own = own_smem + (k & 1) * 2 * D;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        own[d0 + e] = new_k_lo[e];
+                        own[kHalf + d0 + e] = new_k_hi[e];
+                        own[D + d0 + e] = new_v_lo[e];
+                        own[D + kHalf + d0 + e] = new_v_hi[e];
+                    }
+                    if (page >= 0) {
+                        __nv_bfloat16* k_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 0, kvh, pos % kTile);
+                        __nv_bfloat16* v_dst = (__nv_bfloat16*)kv.base + kv_offset(kv, page, 1, kvh, pos % kTile);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) {
+                            k_dst[d0 + e] = new_k_lo[e];
+                            k_dst[kHalf + d0 + e] = new_k_hi[e];
+                            v_dst[d0 + e] = new_v_lo[e];
+                            v_dst[kHalf + d0 + e] = new_v_hi[e];
+                        }
+                    }
+                }
+                if (lane == 0) {
+                    position_bad[k & 1] = position_ok ? 0 : 1;
+                    if (!position_ok && err) atomicOr(err, THN_ERR_POSITION_RANGE);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);              // (release: the warp's stores above are visible to the waiters)
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- the arithmetic
+    const int tq = lane & 3, g = lane >> 2;
+    int it = 0, k = 0;
+    bool ok = true;
+    int pos_next = blockIdx.x < n_pairs ? row_pos[blockIdx.x / kv.n_kv] : 0;
+    for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x, ++k) {
+        const int b = pair / kv.n_kv, kvh = pair % kv.n_kv;
+        const int pos = pos_next;
+        if (pair + gridDim.x < n_pairs) pos_next = row_pos[(pair + gridDim.x) / kv.n_kv];
+        int first_key = 0;
+        if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
+        const int t_first = first_key / kTile, t_last = pos / kTile;
+
+        // ---- q from the preparer
+        if (ok && !*give_up) ok = mbar_wait(q_full, k & 1);
+        const bool alive = ok && !*give_up;
+        uint32_t qf[D / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+            ldmatrix_x4(qf[kk], q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * D + kk * 16 + (lane >> 4) * 8);
+        const bool position_ok = !FUSED || position_bad[k & 1] == 0;
+        __syncwarp();
+        if (lane == 0 && alive) mbar_arrive(q_empty);
+        // FUSED: the warp whose sixteen keys of the last tile include the step's own position
+        // puts that token's key and value into the tile.
+        const bool patches = FUSED && fused.write_cache && warp == (pos % kTile) / 16 && position_ok;
+
+        float o[D / 8][4];
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
+        RowState st;
+        st.init();
+
+        for (int t = t_first; t <= t_last; ++t, ++it) {
+            const int s = it % STAGES;
+            if (ok && !*give_up) ok = mbar_wait(full + s, (it / STAGES) & 1);
+            if (!ok || *give_up) continue;            // keep counting tiles; nothing more is computed
+            unsigned char* k_tile = tiles + (size_t)s * 2 * kTileBytes;
+            unsigned char* v_tile = k_tile + kTileBytes;
+            if (patches && t == t_last) {
+                // the tile may have come from the cache without this step's token (no other warp
+                // reads these rows of the tile)
+                const int in_page = pos % kTile, d0 = lane * E;
+                const __nv_bfloat16* own = own_smem + (k & 1) * 2 * D;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const uint32_t lo_at = swizzled(in_page, d0 + e) + ((d0 + e) & 7) * 2;
+                    const uint32_t hi_at = swizzled(in_page, kHalf + d0 + e) + ((kHalf + d0 + e) & 7) * 2;
+                    *reinterpret_cast<__nv_bfloat16*>(k_tile + lo_at) = own[d0 + e];
+                    *reinterpret_cast<__nv_bfloat16*>(k_tile + hi_at) = own[kHalf + d0 + e];
+                    *reinterpret_cast<__nv_bfloat16*>(v_tile + lo_at) = own[D + d0 + e];
+                    *reinterpret_cast<__nv_bfloat16*>(v_tile + hi_at) = own[D + kHalf + d0 + e];
+                }
+                // the next fetch into this buffer comes through the asynchronous proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+            }
+            const int key0 = t * kTile + warp * 16;
+            float sc[2][4];
+            qk_tile_swizzled<D, 2>(sc, qf, k_tile, warp * 2, lane);
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key0 + n * 8 + tq * 2 + (i & 1);
+                    const bool visible = key <= pos && key >= first_key;
+                    sc[n][i] = visible ? sc[n][i] * scale_log2 : -INFINITY;
+                }
+            uint32_t pf[1][4];
+            softmax_tile<D, 2>(sc, st, o, pf);
+            pv_tile_swizzled<D, 2>(o, pf, v_tile, warp * 2, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + s);
+        }
+
+        // ---- merge the four warps (as attention_decode_kernel does, in scratch of its own)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float l = st.l[r];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const int row = g + 8 * r;
+            if (row < G) {
+                if (tq == 0) {
+                    m_smem[warp * 16 + row] = st.m[r];
+                    l_smem[warp * 16 + row] = l;
+                }
+#pragma unroll
+                for (int nd = 0; nd < D / 8; ++nd)
+                    *reinterpret_cast<float2*>(o_smem + (warp * G + row) * kOPitch + nd * 8 + tq * 2) =
+                        make_float2(o[nd][2 * r], o[nd][2 * r + 1]);
+            }
+        }
+        sync_arithmetic();
+        if ((threadIdx.x & ~31) < 4 * G) {                          // whole warps: the shuffles below take all 32 lanes
+            const bool live = threadIdx.x < 4 * G;
+            const int row = min((int)threadIdx.x >> 2, 15), w = threadIdx.x & 3;
+            const float mine = m_smem[w * 16 + row];
+            float m = mine;
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            const float wgt = m == -INFINITY ? 0.f : merge_exp2(mine - m);
+            float l = l_smem[w * 16 + row] * wgt;
+            const float l1 = l + __shfl_xor_sync(0xffffffffu, l, 1);          // (w0 + w1), (w2 + w3): the order is fixed
+            l = l1 + __shfl_xor_sync(0xffffffffu, l1, 2);
+            if (live) {
+                wgt_smem[row * 4 + w] = wgt;
+                if (w == 0) {
+                    ml_smem[row * 2] = m;
+                    ml_smem[row * 2 + 1] = l;
+                }
+            }
+        }
+        sync_arithmetic();
+        if (ok && !*give_up && position_ok) {
+#pragma unroll 1
+            for (int e = threadIdx.x; e < G * D; e += 128) {
+                const int row = e / D, d = e % D;
+                const float4 wgt = *reinterpret_cast<const float4*>(wgt_smem + row * 4);
+                const float acc = (o_smem[(0 * G + row) * kOPitch + d] * wgt.x + o_smem[(1 * G + row) * kOPitch + d] * wgt.y) +
+                                  (o_smem[(2 * G + row) * kOPitch + d] * wgt.z + o_smem[(3 * G + row) * kOPitch + d] * wgt.w);
+                out[((size_t)b * n_q + kvh * G + row) * D + d] = __float2bfloat16_rn(acc / ml_smem[row * 2 + 1]);
+            }
+        }
+        sync_arithmetic();                                  // the scratch is free for the next pair
+    }
+    if (!ok) {
+        if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
+        *give_up = 1;
+    }
+}
+
 template <int D> constexpr size_t prefill_smem() { return (size_t)(kPrefillRows + 4 * kTile) * (D + 8) * 2; }
 template <int D, int STAGES> constexpr size_t decode_smem() { return (size_t)(16 + 2 * STAGES * kTile) * (D + 8) * 2; }
 
@@ -784,6 +1260,11 @@ int configure_decode() {
     }
     return THN_OK;
 }
+
+// What the last launch of a decode kernel was built with: tile buffers * 10, + 1 if the splits
+// met in a cluster, + 2 for the streaming kernel.  Tests read it to see that they reached the
+// variant they mean to check.
+int g_last_decode_variant = 0;
 
 constexpr int kMaxClusterSplits = 8;      // the portable cluster size; clusters of 16 measured slower than 8 (12.1 -> 14.1 us at batch 1, 4,096 keys)
 int g_decode_cluster = 1;
@@ -845,10 +1326,6 @@ int decode_clusters_resident(int c) {
     return resident[c];
 }
 
-// What the last launch of the decode kernel was built with: tile buffers * 10 + 1 if the splits
-// met in a cluster.  Tests read it to see that they reached the variant they mean to check.
-int g_last_decode_variant = 0;
-
 template <int D, int STAGES, bool FUSED, bool CLUSTER>
 int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                        PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
@@ -868,6 +1345,75 @@ int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, 
     return thn_launch_status(CLUSTER ? "attention_decode (cluster)" : "attention_decode");
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The cache entry as [pages * 2 * n_kv * 64 rows, head_dim] bfloat16 with boxes of 64 values x 64
+// rows and the 128-byte swizzle.
+bool make_kv_map(CUtensorMap* map, const void* base, long long n_pages, int n_kv, int head_dim) {
+    static EncodeTiledFn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            return false;
+        encode = (EncodeTiledFn)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)(n_pages * 2 * n_kv * kTile)};
+    const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kTile};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_decode_stream = 1;           // 0: steps of many pairs keep to attention_decode_kernel
+int g_decode_stream_stages = 3;    // tile buffers of the streaming kernel: 3 or 6
+
+template <int D, int STAGES, bool FUSED>
+int launch_decode_stream(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv,
+                         long long n_pages, int n_seqs, int n_q, float scale, int window, int* err, cudaStream_t stream,
+                         const FusedInput& fused) {
+    const int G = n_q / kv.n_kv;
+    const size_t smem = stream_smem<D>(STAGES, G);
+    static size_t reserved = 0;
+    static int per_sm_for[17] = {0};
+    auto kernel = attention_decode_stream_kernel<D, STAGES, FUSED>;
+    if (smem > reserved) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            thn_set_error("attention_decode (streaming): cannot reserve %zu bytes of shared memory: %s", smem,
+                          cudaGetErrorString(e));
+            return (int)e;
+        }
+        reserved = smem;
+    }
+    if (per_sm_for[G] == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kStreamThreads, smem) != cudaSuccess || n < 1) {
+            cudaGetLastError();
+            n = 1;
+        }
+        per_sm_for[G] = n;
+    }
+    CUtensorMap map;
+    if (!make_kv_map(&map, kv.base, n_pages, kv.n_kv, D)) {
+        thn_set_error("attention_decode (streaming): cannot describe the cache entry to the copy engine");
+        return THN_BAD_ARGUMENT;
+    }
+    // As many blocks as are resident at once, fewer if that spreads the pairs more evenly.
+    const long long n_pairs = (long long)n_seqs * kv.n_kv, resident = (long long)sm_count() * per_sm_for[G];
+    const long long rounds = (n_pairs + resident - 1) / resident;
+    const int grid = (int)((n_pairs + rounds - 1) / rounds);
+    g_last_decode_variant = STAGES * 10 + 2;
+    thn_launch(kernel, dim3(grid), kStreamThreads, smem, stream, map, (__nv_bfloat16*)out, (const __nv_bfloat16*)q,
+               row_slot, row_pos, kv, n_seqs, n_q, scale * kLog2e, window, err, fused);
+    return thn_launch_status("attention_decode (streaming)");
+}
+
 // A block keeps STAGES - 1 tiles on their way while it works on one.  A block that has an SM to
 // itself needs about five in flight for its share of the memory bandwidth; with more blocks on an
 // SM each has less shared memory and needs less.  The deepest pipeline with which the whole grid
@@ -875,13 +1421,22 @@ int launch_decode_with(void* out, float* part_o, float* part_ml, const void* q, 
 template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
-                  cudaStream_t stream, FusedInput fused = FusedInput{}) {
+                  cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0) {
 #define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
     const int n_pairs = n_seqs * kv.n_kv;
     if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster) {
         if (decode_clusters_resident<D, 6, FUSED>(n_splits) >= n_pairs) return launch_decode_with<D, 6, FUSED, true>(THN_DECODE_ARGS);
         if (decode_clusters_resident<D, 3, FUSED>(n_splits) >= n_pairs) return launch_decode_with<D, 3, FUSED, true>(THN_DECODE_ARGS);
         return launch_decode_with<D, 2, FUSED, true>(THN_DECODE_ARGS);
+    }
+    // One block per pair would be next.  With the cache entry's size known, the kernel that
+    // streams several pairs through each resident block takes the step instead.
+    if (n_splits == 1 && n_pages > 0 && g_decode_stream) {
+        if (g_decode_stream_stages >= 6)
+            return launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window,
+                                                     err, stream, fused);
+        return launch_decode_stream<D, 3, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
+                                                 stream, fused);
     }
     const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
     int status;
@@ -908,7 +1463,7 @@ THN_API int thn_attention_mma_supported(int head_dim, int page_size, int n_q, in
            n_q / n_kv <= 16;
 }
 
-// Tile buffers * 10 + (1: cluster) of the most recent decode attention launch of this process.
+// Tile buffers * 10 + (1: cluster, 2: streaming) of the most recent decode attention launch of this process.
 THN_API int thn_attention_decode_last_variant() { return g_last_decode_variant; }
 
 // Rows of a row tile of the prompt kernel (see thn_attention_prefill_bf16).
@@ -972,14 +1527,23 @@ THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_
     return 0;
 }
 
+// 0: steps of many (sequence, kv head) pairs use one block per pair; 1 (default): the streaming
+// kernel.  stages: its tile buffers, 3 or 6.
+THN_API void thn_set_decode_stream(int enabled, int stages) {
+    g_decode_stream = enabled ? 1 : 0;
+    g_decode_stream_stages = stages >= 6 ? 6 : 3;
+}
+
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
+// n_pages: pages of the cache entry (0 if unknown: the kernels that need a map of it are left out).
 // counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the
 // last block of each (sequence, kv head) combines the splits itself; null: a second kernel
 // combines them.
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window, float* scratch, int* counters, int* err, cudaStream_t stream) {
+                                      int window, float* scratch, int* counters, long long n_pages, int* err,
+                                      cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
@@ -992,8 +1556,10 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
     if (head_dim == 64)
-        return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
-    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream);
+        return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
+                                 counters, err, stream, FusedInput{}, n_pages);
+    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
+                              counters, err, stream, FusedInput{}, n_pages);
 }
 
 // The same with the q/k norm, the rotation and the cache write of the step's token inside the
@@ -1006,7 +1572,8 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                                             int table_len, int write_cache, const int* row_slot, const int* row_pos,
                                             void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                             int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                            int window, float* scratch, int* counters, int* err, cudaStream_t stream) {
+                                            int window, float* scratch, int* counters, long long n_pages, int* err,
+                                            cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode_fused: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode_fused: at most 32 splits with counters, got %d",
                   n_splits);
@@ -1024,9 +1591,9 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                      write_cache};
     if (head_dim == 64)
         return launch_decode<64, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                       window, counters, err, stream, fused);
+                                       window, counters, err, stream, fused, n_pages);
     return launch_decode<128, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                    window, counters, err, stream, fused);
+                                    window, counters, err, stream, fused, n_pages);
 }
 
 // ------------------------------------------------------------------ no device allocation
@@ -1087,5 +1654,5 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, err, stream);
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, err, stream);
 }

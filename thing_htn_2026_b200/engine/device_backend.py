@@ -83,9 +83,13 @@ class DeviceBackend:
     # ------------------------------------------------------------------ batches
 
     def open_batch(self, requests: Sequence[Request]) -> List[int]:
+        # Pages are mapped step by step: the prompt's here, a new one whenever a sequence crosses
+        # a page boundary (launch_decode).  A batch is admitted by its full length
+        # (generation.form_batches) and batches run one at a time, so the pages are there when
+        # they are asked for; a windowed group meanwhile gives pages back and maps them again.
         slots = self.cache.open(len(requests))
         try:
-            self.cache.prepare(slots, [tokens_needed(r, 1) for r in requests])
+            self.cache.prepare(slots, [len(r.tokens) for r in requests])
         except Exception:
             self.cache.close(slots)
             raise
@@ -170,6 +174,7 @@ class DeviceBackend:
         context_class, max_context = ops.context_class(longest)
         if self.use_graphs and (batch, context_class) not in self.graphs:
             self._capture(batch, context_class, max_context)
+        self.cache.prepare(list(slots), [1] * batch)          # a block-table update only at page boundaries
         self._set_composition(slots)
         if self.use_graphs:
             self.graphs[(batch, context_class)].replay()

@@ -52,7 +52,8 @@ _SIGNATURES = {
                                c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_attention_decode_fused_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                        c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
+                                        c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -64,7 +65,8 @@ _SIGNATURES = {
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
+                                  c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -98,6 +100,10 @@ def lib():
         loaded.thn_set_decode_cluster.argtypes = [c_int]
         loaded.thn_set_decode_cluster.restype = None
         loaded.thn_set_decode_cluster(0 if os.environ.get("THN_DECODE_CLUSTER", "1").strip() in ("0", "false", "off") else 1)
+        loaded.thn_set_decode_stream.argtypes = [c_int, c_int]
+        loaded.thn_set_decode_stream.restype = None
+        loaded.thn_set_decode_stream(0 if os.environ.get("THN_DECODE_STREAM", "1").strip() in ("0", "false", "off") else 1,
+                                     int(os.environ.get("THN_DECODE_STREAM_STAGES", 3)))
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
         loaded.thn_attention_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
@@ -604,7 +610,8 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     out = torch.empty_like(q)
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
-          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), _ptr(err), _stream())
+          n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
+          _ptr(err), _stream())
     return out
 
 
@@ -639,7 +646,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
           _code(q_gain, "qk gains"), float(eps), _ptr(rotary.cos), _ptr(rotary.sin), rotary.cos.shape[0],
           int(bool(write_cache)), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_seqs, n_q, n_splits, float(scale),
-          int(window or 0), _ptr(scratch), _ptr(counters), _ptr(err), _stream())
+          int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0], _ptr(err), _stream())
     return out
 
 
