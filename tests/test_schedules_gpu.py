@@ -61,7 +61,7 @@ def test_decode_attention_with_many_pairs_one_block_per_pair(n_seqs, stages):
     dtype = torch.bfloat16
     lengths = spread_lengths(n_seqs)
     try:
-        o.lib().thn_set_decode_stream(0 if stages == 3 else 1, stages)
+        o.lib().thn_set_decode_stream(0 if stages == 3 else 1, stages)       # off; or on with the deeper ring
         got, want = kernels.attention_case("decode", dtype, 32, 8, 128, lengths, [1] * n_seqs, None)
         variant = o.lib().thn_attention_decode_last_variant()
     finally:
@@ -92,6 +92,95 @@ def test_fused_decode_attention_with_many_pairs(n_seqs):
         assert ops().lib().thn_attention_decode_last_variant() % 10 == 0
     finally:
         ops().lib().thn_set_decode_stream(1, 3)
+
+
+@pytest.fixture
+def streaming_always():
+    """Every unsplit single-token step goes to the streaming kernel, however few its pairs."""
+    o = ops()
+    o.lib().thn_set_decode_stream(2, 3)
+    yield
+    o.lib().thn_set_decode_stream(1, 3)
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 64, None), (32, 8, 128, None), (6, 3, 64, 70), (3, 1, 128, 24),
+                                               (16, 1, 64, None), (5, 5, 128, 200), (16, 1, 128, None), (32, 2, 128, 90)])
+def test_streaming_decode_attention_at_other_sizes(streaming_always, n_q, n_kv, D, window):
+    """The streaming kernel at the sizes and windows of the split kernel's test: both head
+    sizes, groups of 1 to 16 heads, windows inside a page and across pages; and in its fused
+    form against the two separate kernels, bit for bit."""
+    lengths = [700, 64, 65, 1, 333, 128]
+    got, want = kernels.attention_case("decode1", torch.bfloat16, n_q, n_kv, D, lengths, [1] * len(lengths), window)
+    assert ops().lib().thn_attention_decode_last_variant() == 32
+    kernels.close(got, want, torch.bfloat16, "streaming decode attention")
+
+
+def test_streaming_decode_attention_finds_a_far_key_and_the_windows_edge(streaming_always, monkeypatch):
+    monkeypatch.setenv("THN_DECODE_SPLITS", "1")
+    kernels.test_attention_finds_a_far_key("decode", torch.bfloat16)
+    assert ops().lib().thn_attention_decode_last_variant() == 32
+    kernels.test_attention_window_edge("decode", torch.bfloat16)
+    assert ops().lib().thn_attention_decode_last_variant() == 32
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,window", [(8, 2, 128, None), (6, 6, 64, None), (16, 1, 128, 100), (12, 2, 64, None)])
+def test_streaming_fused_decode_attention_at_other_sizes(streaming_always, monkeypatch, n_q, n_kv, D, window):
+    monkeypatch.setenv("THN_DECODE_SPLITS", "1")
+    kernels.fused_decode_case(n_q, n_kv, D, window, torch.bfloat16, [129, 64, 1, 300, 77, 640])
+    assert ops().lib().thn_attention_decode_last_variant() == 32
+
+
+@pytest.mark.parametrize("fused", [False, True], ids=["plain", "fused"])
+def test_streaming_decode_attention_gives_the_same_bits_every_time(fused):
+    """The streaming kernel's tile buffers go round between the loader's copies (asynchronous
+    proxy) and the warps' reads (generic proxy); handed back a moment too early, a buffer was
+    once refilled under a read, in one launch out of four and only with two blocks on an SM.
+    Two hundred launches on the same cache must all give the bits of the first, and those
+    must be the bits of the kernel that takes one block per pair."""
+    o = ops()
+    from thing_htn_2026_b200.config.base import PartSpec
+    from thing_htn_2026_b200.parts import Runtime, part_class
+    dtype, n_seqs, n_q, n_kv, D = torch.bfloat16, 48, 32, 8, 128
+    lengths = spread_lengths(n_seqs)
+    fix = kernels.PagedFixture(n_kv, D, lengths, dtype)
+    old = [n - 1 for n in lengths]
+    live = [i for i, n in enumerate(old) if n > 0]
+    keep = fix.slots
+    fix.slots = [keep[i] for i in live]
+    rows, cu = fix.rows([old[i] for i in live])
+    kernels.write_kv(fix, rows, kernels.rand((cu[-1], n_kv, D), dtype, 80), kernels.rand((cu[-1], n_kv, D), dtype, 81), n_q)
+    fix.advance(rows, [old[i] for i in live])
+    fix.slots = keep
+    rows, cu = fix.rows([1] * n_seqs)
+    err = o.new_error_word(DEV)
+    scale = D ** -0.5
+    if fused:
+        rope = part_class("position", "rope")(PartSpec("rope", {"head_dim": D, "theta": 1e4}), Runtime(dtype, torch.device(DEV), {}))
+        rope.ensure(1024)
+        qkv = kernels.rand((n_seqs, (n_q + 2 * n_kv) * D), dtype, 82, 2.0).to(DEV)
+        gain = (1 + 0.3 * torch.randn(D, generator=torch.Generator().manual_seed(83))).to(DEV)
+
+        def launch():
+            return o.qkv_attention(qkv, gain, gain, 1e-6, rope.tables(), rows, fix.kv, n_q, scale, None, True, err)
+    else:
+        kernels.write_kv(fix, rows, kernels.rand((n_seqs, n_kv, D), dtype, 84), kernels.rand((n_seqs, n_kv, D), dtype, 85), n_q)
+        q = kernels.rand((n_seqs, n_q * D), dtype, 86).to(DEV)
+
+        def launch():
+            return o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, None, err, n_splits=1)
+    outs = [launch() for _ in range(200)]
+    assert o.lib().thn_attention_decode_last_variant() == 32
+    try:
+        o.lib().thn_set_decode_stream(0, 3)
+        one_block_per_pair = launch()
+        assert o.lib().thn_attention_decode_last_variant() % 10 == 0
+    finally:
+        o.lib().thn_set_decode_stream(1, 3)
+    assert int(err.item()) == 0
+    differing = [i for i, out in enumerate(outs) if not torch.equal(out, outs[0])]
+    assert not differing, f"launches {differing[:10]} of 200 differ from the first"
+    worst = (outs[0].float() - one_block_per_pair.float()).abs().max().item()
+    assert worst <= 2e-3, f"differs from the one-block-per-pair kernel by {worst:.3e}"
 
 
 def test_decode_attention_few_pairs_meets_in_a_cluster():

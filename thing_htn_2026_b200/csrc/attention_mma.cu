@@ -810,8 +810,14 @@ __device__ __forceinline__ void tma_tile(void* dst, const CUtensorMap* map, uint
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
-// the four arithmetic warps among themselves (barrier 0 is __syncthreads)
-__device__ __forceinline__ void sync_arithmetic() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// The four arithmetic warps among themselves (barrier 0 is __syncthreads).  The warps come here
+// from branches that only some of their lanes took, and unlike __syncthreads an asm statement
+// does not make the compiler bring them together first: so the warp converges explicitly, and
+// the barrier is the form that counts threads, not the one that wants whole warps.
+__device__ __forceinline__ void sync_arithmetic() {
+    __syncwarp();
+    asm volatile("barrier.sync 1, 128;" ::: "memory");
+}
 
 // Byte offset of the 16 bytes that hold values [d, d + 8) of row `row` in a tile that came as
 // boxes of 64 values x 64 rows with the 128-byte swizzle: a row of a box is 128 bytes, its eight
@@ -1098,7 +1104,11 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
         const int t_first = first_key / kTile, t_last = pos / kTile;
 
         // ---- q from the preparer
+        // (The lanes of a warp leave a wait one by one; what follows, ldmatrix and mma.sync, must
+        // be executed by the whole warp together, and an asm statement does not make the compiler
+        // bring the lanes together: hence the __syncwarp after every wait.)
         if (ok && !*give_up) ok = mbar_wait(q_full, k & 1);
+        __syncwarp();
         const bool alive = ok && !*give_up;
         uint32_t qf[D / 16][4];
 #pragma unroll
@@ -1106,7 +1116,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
             ldmatrix_x4(qf[kk], q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * D + kk * 16 + (lane >> 4) * 8);
         const bool position_ok = !FUSED || position_bad[k & 1] == 0;
         __syncwarp();
-        if (lane == 0 && alive) mbar_arrive(q_empty);
+        if (lane == 0 && alive) mbar_arrive(q_empty);     // (the preparer writes q with plain stores: the same proxy)
         // FUSED: the warp whose sixteen keys of the last tile include the step's own position
         // puts that token's key and value into the tile.
         const bool patches = FUSED && fused.write_cache && warp == (pos % kTile) / 16 && position_ok;
@@ -1122,6 +1132,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
         for (int t = t_first; t <= t_last; ++t, ++it) {
             const int s = it % STAGES;
             if (ok && !*give_up) ok = mbar_wait(full + s, (it / STAGES) & 1);
+            ok = __all_sync(0xffffffffu, ok);         // one decision for the warp, and the lanes together again
             if (!ok || *give_up) continue;            // keep counting tiles; nothing more is computed
             unsigned char* k_tile = tiles + (size_t)s * 2 * kTileBytes;
             unsigned char* v_tile = k_tile + kTileBytes;
@@ -1157,6 +1168,12 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
             uint32_t pf[1][4];
             softmax_tile<D, 2>(sc, st, o, pf);
             pv_tile_swizzled<D, 2>(o, pf, v_tile, warp * 2, lane);
+            // The buffer goes back to the loader, whose next copy into it is made by the
+            // asynchronous proxy, while these reads were made by the generic one: the barrier
+            // alone does not order the two, the proxy fence does.  (Without it one run in four of
+            // a 48-sequence step read sixteen columns of a V tile that the next copy had already
+            // reached, with two blocks on an SM.)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + s);
         }
@@ -1370,8 +1387,9 @@ bool make_kv_map(CUtensorMap* map, const void* base, long long n_pages, int n_kv
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_decode_stream = 1;           // 0: steps of many pairs keep to attention_decode_kernel
+int g_decode_stream = 1;           // 0: never; 1: when the pairs are more than its resident blocks; 2: whenever one split is asked for
 int g_decode_stream_stages = 3;    // tile buffers of the streaming kernel: 3 or 6
+constexpr int kNotTaken = -1;      // launch_decode_stream leaves the step to the caller
 
 template <int D, int STAGES, bool FUSED>
 int launch_decode_stream(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv,
@@ -1406,6 +1424,9 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
     }
     // As many blocks as are resident at once, fewer if that spreads the pairs more evenly.
     const long long n_pairs = (long long)n_seqs * kv.n_kv, resident = (long long)sm_count() * per_sm_for[G];
+    // With a block for every pair there is nothing to stream across; one block per pair of the
+    // kernel above was then as fast or a little faster (2.74 against 2.77 ms per step at batch 32).
+    if (n_pairs <= resident && g_decode_stream < 2) return kNotTaken;
     const long long rounds = (n_pairs + resident - 1) / resident;
     const int grid = (int)((n_pairs + rounds - 1) / rounds);
     g_last_decode_variant = STAGES * 10 + 2;
@@ -1432,11 +1453,12 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // One block per pair would be next.  With the cache entry's size known, the kernel that
     // streams several pairs through each resident block takes the step instead.
     if (n_splits == 1 && n_pages > 0 && g_decode_stream) {
-        if (g_decode_stream_stages >= 6)
-            return launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window,
-                                                     err, stream, fused);
-        return launch_decode_stream<D, 3, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
-                                                 stream, fused);
+        const int taken = g_decode_stream_stages >= 6
+            ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
+                                                stream, fused)
+            : launch_decode_stream<D, 3, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
+                                                stream, fused);
+        if (taken != kNotTaken) return taken;
     }
     const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
     int status;
@@ -1527,10 +1549,11 @@ THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_
     return 0;
 }
 
-// 0: steps of many (sequence, kv head) pairs use one block per pair; 1 (default): the streaming
-// kernel.  stages: its tile buffers, 3 or 6.
-THN_API void thn_set_decode_stream(int enabled, int stages) {
-    g_decode_stream = enabled ? 1 : 0;
+// Which unsplit single-token steps the streaming kernel takes: 0: none (one block per pair);
+// 1 (default): those with more (sequence, kv head) pairs than it has resident blocks; 2: all.
+// stages: its tile buffers, 3 or 6.
+THN_API void thn_set_decode_stream(int mode, int stages) {
+    g_decode_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode;
     g_decode_stream_stages = stages >= 6 ? 6 : 3;
 }
 

@@ -102,7 +102,7 @@ def lib():
         loaded.thn_set_decode_cluster(0 if os.environ.get("THN_DECODE_CLUSTER", "1").strip() in ("0", "false", "off") else 1)
         loaded.thn_set_decode_stream.argtypes = [c_int, c_int]
         loaded.thn_set_decode_stream.restype = None
-        loaded.thn_set_decode_stream(0 if os.environ.get("THN_DECODE_STREAM", "1").strip() in ("0", "false", "off") else 1,
+        loaded.thn_set_decode_stream(int(os.environ.get("THN_DECODE_STREAM", 1)),
                                      int(os.environ.get("THN_DECODE_STREAM_STAGES", 3)))
         loaded.thn_choose_tokens_scratch_floats.argtypes = [c_int, c_int]
         loaded.thn_choose_tokens_scratch_floats.restype = c_longlong
