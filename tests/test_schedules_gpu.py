@@ -33,15 +33,26 @@ def spread_lengths(n_seqs, longest=700):
 
 # ----------------------------------------------------------------------------- decode attention, many pairs
 
+@pytest.fixture
+def streaming_always():
+    """Every unsplit single-token step goes to the streaming kernel, however few its pairs."""
+    o = ops()
+    o.lib().thn_set_decode_stream(2, 3)
+    yield
+    o.lib().thn_set_decode_stream(1, 3)
+
+
+
 seen_variants = {}
 
 
 @pytest.mark.parametrize("splits", ["", "1"])
 @pytest.mark.parametrize("n_seqs", [40, 48, 56, 64])
-def test_decode_attention_with_many_pairs(n_seqs, splits):
+def test_decode_attention_with_many_pairs(n_seqs, splits, streaming_always):
     """32 query heads on 8 kv heads of 128 (the Qwen3-4B attention) for 40 to 64 sequences:
-    320 to 512 (sequence, kv head) pairs, more than fit the GPU as clusters, so each pair is
-    one block with six, three or two tile buffers, and at the top a second pass."""
+    320 to 512 (sequence, kv head) pairs, more than fit the GPU as clusters, through the
+    streaming kernel (which by itself takes the steps that would need a second pass: 56 and 64
+    sequences here)."""
     o = ops()
     dtype = torch.bfloat16
     lengths = spread_lengths(n_seqs)
@@ -61,7 +72,7 @@ def test_decode_attention_with_many_pairs_one_block_per_pair(n_seqs, stages):
     dtype = torch.bfloat16
     lengths = spread_lengths(n_seqs)
     try:
-        o.lib().thn_set_decode_stream(0 if stages == 3 else 1, stages)       # off; or on with the deeper ring
+        o.lib().thn_set_decode_stream(0 if stages == 3 else 2, stages)       # off; or always, with the deeper ring
         got, want = kernels.attention_case("decode", dtype, 32, 8, 128, lengths, [1] * n_seqs, None)
         variant = o.lib().thn_attention_decode_last_variant()
     finally:
@@ -85,22 +96,19 @@ def test_decode_attention_many_pairs_took_every_branch():
 @pytest.mark.parametrize("n_seqs", [40, 64])
 def test_fused_decode_attention_with_many_pairs(n_seqs):
     kernels.fused_decode_case(32, 8, 128, None, torch.float32, spread_lengths(n_seqs))
-    assert ops().lib().thn_attention_decode_last_variant() % 10 == 2
+    assert ops().lib().thn_attention_decode_last_variant() % 10 == (2 if n_seqs == 64 else 0)
+    try:
+        ops().lib().thn_set_decode_stream(2, 3)
+        kernels.fused_decode_case(32, 8, 128, None, torch.float32, spread_lengths(n_seqs))
+        assert ops().lib().thn_attention_decode_last_variant() % 10 == 2
+    finally:
+        ops().lib().thn_set_decode_stream(1, 3)
     try:
         ops().lib().thn_set_decode_stream(0, 3)
         kernels.fused_decode_case(32, 8, 128, None, torch.float32, spread_lengths(n_seqs))
         assert ops().lib().thn_attention_decode_last_variant() % 10 == 0
     finally:
         ops().lib().thn_set_decode_stream(1, 3)
-
-
-@pytest.fixture
-def streaming_always():
-    """Every unsplit single-token step goes to the streaming kernel, however few its pairs."""
-    o = ops()
-    o.lib().thn_set_decode_stream(2, 3)
-    yield
-    o.lib().thn_set_decode_stream(1, 3)
 
 
 @pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 64, None), (32, 8, 128, None), (6, 3, 64, 70), (3, 1, 128, 24),
@@ -168,6 +176,7 @@ def test_streaming_decode_attention_gives_the_same_bits_every_time(fused):
 
         def launch():
             return o.attention_decode_bf16(q, rows, fix.kv, n_q, scale, None, err, n_splits=1)
+    o.lib().thn_set_decode_stream(2, 3)
     outs = [launch() for _ in range(200)]
     assert o.lib().thn_attention_decode_last_variant() == 32
     try:

@@ -1424,9 +1424,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
     }
     // As many blocks as are resident at once, fewer if that spreads the pairs more evenly.
     const long long n_pairs = (long long)n_seqs * kv.n_kv, resident = (long long)sm_count() * per_sm_for[G];
-    // With a block for every pair there is nothing to stream across; one block per pair of the
-    // kernel above was then as fast or a little faster (2.74 against 2.77 ms per step at batch 32).
-    if (n_pairs <= resident && g_decode_stream < 2) return kNotTaken;
+    if (n_pairs <= resident && g_decode_stream < 2) return kNotTaken;     // nothing to stream across
     const long long rounds = (n_pairs + resident - 1) / resident;
     const int grid = (int)((n_pairs + rounds - 1) / rounds);
     g_last_decode_variant = STAGES * 10 + 2;
@@ -1452,7 +1450,12 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     }
     // One block per pair would be next.  With the cache entry's size known, the kernel that
     // streams several pairs through each resident block takes the step instead.
-    if (n_splits == 1 && n_pages > 0 && g_decode_stream) {
+    // It pays where one block per pair would need a second pass (more pairs than the GPU holds
+    // such blocks with two tile buffers each); below that, one block per pair was as fast or
+    // faster: 2.74 / 2.93 / 3.09 against 2.77 / 3.04 / 3.14 ms per step at batch 32 / 40 / 48,
+    // and 3.43 / 3.47 against 3.24 / 3.34 ms at batch 56 / 64 (Qwen3-4B sizes, 8 kv heads).
+    const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
+    if (n_splits == 1 && n_pages > 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && second_pass))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
                                                 stream, fused)

@@ -78,6 +78,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         else if (now - start > kWaitLimitNs) return false;
     }
 }
+// The same without parking: for the one thread that issues the products, whose every wait stands
+// between the softmax warps and the tensor core.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    unsigned long long start = 0;
+    for (int spins = 0;; ++spins) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spins & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > kWaitLimitNs) return false;
+        }
+    }
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -274,12 +299,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer.  S of tile it + 1 is multiplied while the softmax warps work on
         // tile it; O += P V of tile it follows as soon as its P is ready.
-        bool ok = mbar_wait(q_full, 0);
+        bool ok = mbar_wait_spin(q_full, 0);
         const int n_it = t_last - t_first + 1;
         const uint32_t q_addr = smem_addr(q_smem);
         auto qk = [&](int it) {          // S[it & 1] = Q K(it)^T
             const int s = it % kStages;
-            if (!mbar_wait(k_full + s, (it / kStages) & 1)) return false;
+            if (!mbar_wait_spin(k_full + s, (it / kStages) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t k_addr = smem_addr(kv_smem + (size_t)s * kStageBytes);
             // eight k steps of 16 d; d 0-63 in the first swizzled block, 64-127 in the second
@@ -299,10 +324,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 ok = qk(it + 1);
                 if (!ok) break;
             }
-            ok = mbar_wait(p_ready, it & 1);      // P is in tensor memory; O has been rescaled
+            ok = mbar_wait_spin(p_ready, it & 1);      // P is in tensor memory; O has been rescaled
             if (!ok) break;
             const int s = it % kStages;
-            ok = mbar_wait(v_full + s, (it / kStages) & 1);
+            ok = mbar_wait_spin(v_full + s, (it / kStages) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t v_addr = smem_addr(kv_smem + (size_t)s * kStageBytes) + kKBytes;
@@ -331,6 +356,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         int it = 0;
         for (int t = t_first; t <= t_last && !*give_up; ++t, ++it) {
             ok = mbar_wait(s_full + (it & 1), (it >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);        // the lanes leave a wait one by one; tcgen05.ld wants the warp together
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float s[64];
@@ -387,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             // previous O += P V must be complete first.  tcgen05.ld/st are warp-wide, so the whole
             // warp goes if any of its rows must.
             if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                ok = mbar_wait(o_full, (it - 1) & 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(o_full, (it - 1) & 1));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -417,8 +443,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
         }
-        if (ok && !*give_up && it > 0) {
-            ok = mbar_wait(o_full, (it - 1) & 1);
+        if (ok && !*give_up && it > 0) {             // (ok is the same in every lane: see the waits above)
+            ok = __all_sync(0xffffffffu, mbar_wait(o_full, (it - 1) & 1));
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = 1.0f / run_sum;
@@ -484,7 +510,6 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 
 }  // namespace
 
-// 1 if thn_attention_prefill_tcgen05 takes this shape.
 // Test switch (see g_test_skip_kv_loads): nonzero makes every later launch on the current device
 // run into its wait limit.  Returns a status.
 THN_API int thn_attention_tcgen05_test_skip_loads(int on) {
@@ -497,6 +522,7 @@ THN_API int thn_attention_tcgen05_test_skip_loads(int on) {
     return THN_OK;
 }
 
+// 1 if thn_attention_prefill_tcgen05 takes this shape.
 THN_API int thn_attention_tcgen05_supported(int head_dim, int page_size, int n_q, int n_kv) {
     return head_dim == D && page_size == kKeys && n_kv > 0 && n_q % n_kv == 0;
 }

@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
         for (int local = 0; local < run.n_seg && !*give_up; ++local) {
             const Segment seg = run.at(local);
             const int buf = local & 1;
-            if (!mbar_wait(acc_full + buf, (local >> 1) & 1)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, (local >> 1) & 1))) {      // all lanes together before tcgen05.ld
                 if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 *give_up = 1;
                 break;
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
 #pragma unroll
         for (int j = 0; j < NX; ++j) acc[j] = 0.f;
         if (c1 > c0) {
-            if (mbar_wait(acc_full, 0)) {
+            if (__all_sync(0xffffffffu, mbar_wait(acc_full, 0))) {      // all lanes together before tcgen05.ld
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll

@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
             const int buf = local & 1;
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * kTileCols;
             const int row = m0 + quarter * 32 + lane;
-            if (!mbar_wait(acc_full + buf, (local >> 1) & 1)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, (local >> 1) & 1))) {      // all lanes together before tcgen05.ld
                 if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 *give_up = 1;
                 break;
