@@ -190,7 +190,7 @@ def test_greedy_across_classes_of_context_length(tiny_models, monkeypatch):
     assert [len(t) for t in tokens] == [180, 40]
     for prompt, emitted in zip(prompts, tokens):
         check_greedy(tiny_models[name], "bfloat16", prompt, emitted)
-    assert {(2, 0), (2, 1), (1, 1), (1, 2)} <= set(engine.backend.graphs), sorted(engine.backend.graphs)
+    assert {(2, 0), (2, 1), (1, 1), (1, 2)} <= {k[:2] for k in engine.backend.graphs}, sorted(engine.backend.graphs)
     engine.backend.cache.check()
 
 

@@ -46,3 +46,11 @@ def test_counter_buffer_refuses_to_grow():
     import pytest
     with pytest.raises(ops.KernelError, match="arrival counters"):
         ops._counter_buffer(ops.COUNTER_SLOTS + 1, "cpu")
+
+
+def test_lengths_differ_is_a_coarse_class():
+    assert not ops.lengths_differ([640] * 8)
+    assert not ops.lengths_differ([640, 600, 520, 481])         # within a quarter of the longest
+    assert ops.lengths_differ([640, 479])
+    assert ops.lengths_differ([2048, 64, 1000])
+    assert not ops.lengths_differ([1])

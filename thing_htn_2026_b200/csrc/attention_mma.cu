@@ -871,12 +871,13 @@ constexpr size_t stream_smem(int stages, int G) {
     return (size_t)stages * 2 * kTile * D * 2 + 16 * D * 2 + 4 * D * 2 + (size_t)(128 + 4 * G * (D + 8) + 64 + 32) * 4 +
            (size_t)(2 * stages + 2) * 8 + 16;
 }
+constexpr int kStreamRankedSeqs = 256;      // sequences up to which the pairs are dealt out by length (6 bytes each)
 
 template <int D, int STAGES, bool FUSED>
 __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_decode_stream_kernel(
     const __grid_constant__ CUtensorMap map_kv, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
     const int* __restrict__ row_slot, const int* __restrict__ row_pos, PagedKV kv, int n_seqs, int n_q,
-    float scale_log2, int window, int* __restrict__ err, FusedInput fused) {
+    float scale_log2, int window, int* __restrict__ err, FusedInput fused, int by_length) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int kOPitch = D + 8;
@@ -897,6 +898,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
     uint64_t* q_empty = q_full + 1;                                     // the four warps hold q in registers
     volatile int* give_up = reinterpret_cast<volatile int*>(q_empty + 1);
     volatile int* position_bad = give_up + 1;                           // [2] by pair parity
+    unsigned short* by_rank = reinterpret_cast<unsigned short*>(const_cast<int*>(position_bad + 2) + 1);   // [n_seqs] (by_length)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int n_pairs = n_seqs * kv.n_kv;
@@ -910,7 +912,37 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
         *give_up = (smem_u32(tiles) & 1023u) ? 1 : 0;      // the swizzle's arithmetic needs the alignment
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // by_length: the sequences ranked by their length, longest first (ties by index), every
+    // block for itself: by_rank[rank] = sequence.  The pairs are then dealt out in that order,
+    // forwards in even rounds and backwards in odd ones, so that a block's pairs add up to about
+    // the same number of keys whatever the lengths are.
+    if (by_length) {
+        int* lengths = reinterpret_cast<int*>(by_rank + ((n_seqs + 1) & ~1));       // [n_seqs], read once from global memory
+        for (int b = threadIdx.x; b < n_seqs; b += kStreamThreads) lengths[b] = row_pos[b];
+        __syncthreads();
+        for (int b = threadIdx.x; b < n_seqs; b += kStreamThreads) {
+            const int mine = lengths[b];
+            int rank = 0;
+            for (int other = 0; other < n_seqs; ++other) {
+                const int theirs = lengths[other];
+                rank += (theirs > mine || (theirs == mine && other < b)) ? 1 : 0;
+            }
+            by_rank[rank] = (unsigned short)b;
+        }
+    }
     __syncthreads();
+    // The k-th pair of this block: (sequence, kv head), or sequence -1 when the block has no k-th pair.
+    const int n_rounds = (n_pairs + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto pair_of = [&](int k, int& b, int& kvh) {
+        int item = k * (int)gridDim.x + ((k & 1) && by_length ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (k >= n_rounds || item >= n_pairs) {
+            b = -1;
+            kvh = 0;
+            return;
+        }
+        kvh = item % kv.n_kv;
+        b = by_length ? (int)by_rank[item / kv.n_kv] : item / kv.n_kv;
+    };
     if (*give_up) {
         if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
         return;
@@ -920,20 +952,21 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
         // ---------------------------------------------------------------- the loader
         int it = 0;                                        // tiles requested so far by this block
         bool ok = true;
-        int pair = blockIdx.x;
-        int pos_next = 0, slot_next = 0;
-        if (pair < n_pairs) {
-            pos_next = row_pos[pair / kv.n_kv];
-            slot_next = row_slot[pair / kv.n_kv];
+        int b_next, kvh_next, pos_next = 0, slot_next = 0;
+        pair_of(0, b_next, kvh_next);
+        if (b_next >= 0) {
+            pos_next = row_pos[b_next];
+            slot_next = row_slot[b_next];
         }
-        for (; pair < n_pairs && ok && !*give_up; pair += gridDim.x) {
-            const int kvh = pair % kv.n_kv;
+        for (int k = 0; k < n_rounds && ok && !*give_up; ++k) {
+            const int b = b_next, kvh = kvh_next;
             const int pos = pos_next, slot = slot_next;
-            const int after = pair + gridDim.x;
-            if (after < n_pairs) {                          // a pair ahead: on its way while this pair's tiles are requested
-                pos_next = row_pos[after / kv.n_kv];
-                slot_next = row_slot[after / kv.n_kv];
+            pair_of(k + 1, b_next, kvh_next);
+            if (b_next >= 0) {                              // a pair ahead: on its way while this pair's tiles are requested
+                pos_next = row_pos[b_next];
+                slot_next = row_slot[b_next];
             }
+            if (b < 0) continue;
             int first_key = 0;
             if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
             const int t_first = first_key / kTile, t_last = pos / kTile;
@@ -996,14 +1029,16 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
         }
         __syncwarp();
         bool ok = true;
-        int k = 0;
-        for (int pair = blockIdx.x; pair < n_pairs && ok && !*give_up; pair += gridDim.x, ++k) {
-            const int b = pair / kv.n_kv, kvh = pair % kv.n_kv;
+        for (int round = 0, k = 0; round < n_rounds && ok && !*give_up; ++round) {
+            int b, kvh;
+            pair_of(round, b, kvh);
+            if (b < 0) continue;
+            const int k_now = k++;
             // what the pair needs from global memory is requested before the wait for q's buffer
             __nv_bfloat16 raw_lo[4][E], raw_hi[4][E];                     // up to four heads in flight
             const int pos = FUSED ? row_pos[b] : 0;
             const bool position_ok = !FUSED || pos < fused.table_len;
-            if (lane == 0) ok = mbar_wait(q_empty, (k & 1) ^ 1);
+            if (lane == 0) ok = mbar_wait(q_empty, (k_now & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
             if (!ok) {
                 if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
@@ -1059,7 +1094,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
                     }
                     const int page = position_ok ? (kv.block_table + (size_t)row_slot[b] * kv.bt_stride)[pos / kTile] : -1;
                     norm_rotate_head<D>(raw_k_lo, raw_k_hi, kg_lo, kg_hi, fused.eps, c, sn, new_k_lo, new_k_hi);
-                    __nv_bfloat16* own = own_smem + (k & 1) * 2 * D;
+                    __nv_bfloat16* own = own_smem + (k_now & 1) * 2 * D;
 #pragma unroll
                     for (int e = 0; e < E; ++e) {
                         own[d0 + e] = new_k_lo[e];
@@ -1080,7 +1115,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
                     }
                 }
                 if (lane == 0) {
-                    position_bad[k & 1] = position_ok ? 0 : 1;
+                    position_bad[k_now & 1] = position_ok ? 0 : 1;
                     if (!position_ok && err) atomicOr(err, THN_ERR_POSITION_RANGE);
                 }
             }
@@ -1094,11 +1129,15 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
     const int tq = lane & 3, g = lane >> 2;
     int it = 0, k = 0;
     bool ok = true;
-    int pos_next = blockIdx.x < n_pairs ? row_pos[blockIdx.x / kv.n_kv] : 0;
-    for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x, ++k) {
-        const int b = pair / kv.n_kv, kvh = pair % kv.n_kv;
+    int b_next, kvh_next;
+    pair_of(0, b_next, kvh_next);
+    int pos_next = b_next >= 0 ? row_pos[b_next] : 0;
+    for (int round = 0; round < n_rounds; ++round) {
+        const int b = b_next, kvh = kvh_next;
         const int pos = pos_next;
-        if (pair + gridDim.x < n_pairs) pos_next = row_pos[(pair + gridDim.x) / kv.n_kv];
+        pair_of(round + 1, b_next, kvh_next);
+        if (b_next >= 0) pos_next = row_pos[b_next];
+        if (b < 0) continue;
         int first_key = 0;
         if (window > 0 && pos - window + 1 > 0) first_key = pos - window + 1;
         const int t_first = first_key / kTile, t_last = pos / kTile;
@@ -1228,6 +1267,7 @@ __global__ void __launch_bounds__(kStreamThreads, D == 128 ? 2 : 3) attention_de
             }
         }
         sync_arithmetic();                                  // the scratch is free for the next pair
+        ++k;
     }
     if (!ok) {
         if (lane == 0 && err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
@@ -1389,14 +1429,18 @@ bool make_kv_map(CUtensorMap* map, const void* base, long long n_pages, int n_kv
 
 int g_decode_stream = 1;           // 0: never; 1: when the pairs are more than its resident blocks; 2: whenever one split is asked for
 int g_decode_stream_stages = 3;    // tile buffers of the streaming kernel: 3 or 6
+int g_decode_stream_by_length = 1; // its pairs dealt out by length (0: in index order)
 constexpr int kNotTaken = -1;      // launch_decode_stream leaves the step to the caller
 
 template <int D, int STAGES, bool FUSED>
 int launch_decode_stream(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv,
                          long long n_pages, int n_seqs, int n_q, float scale, int window, int* err, cudaStream_t stream,
-                         const FusedInput& fused) {
+                         const FusedInput& fused, int lengths_differ) {
     const int G = n_q / kv.n_kv;
-    const size_t smem = stream_smem<D>(STAGES, G);
+    // Ranking costs each block about a microsecond at its start and gains 9 % on lengths spread
+    // over 64 to 2,048 keys: it is done where the caller says that the lengths differ.
+    const int by_length = g_decode_stream_by_length && lengths_differ && n_seqs <= kStreamRankedSeqs;
+    const size_t smem = stream_smem<D>(STAGES, G) + (by_length ? (size_t)((n_seqs + 1) & ~1) * 2 + (size_t)n_seqs * 4 : 0);
     static size_t reserved = 0;
     static int per_sm_for[17] = {0};
     auto kernel = attention_decode_stream_kernel<D, STAGES, FUSED>;
@@ -1429,7 +1473,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
     const int grid = (int)((n_pairs + rounds - 1) / rounds);
     g_last_decode_variant = STAGES * 10 + 2;
     thn_launch(kernel, dim3(grid), kStreamThreads, smem, stream, map, (__nv_bfloat16*)out, (const __nv_bfloat16*)q,
-               row_slot, row_pos, kv, n_seqs, n_q, scale * kLog2e, window, err, fused);
+               row_slot, row_pos, kv, n_seqs, n_q, scale * kLog2e, window, err, fused, by_length);
     return thn_launch_status("attention_decode (streaming)");
 }
 
@@ -1440,7 +1484,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
 template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
-                  cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0) {
+                  cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0, int lengths_differ = 1) {
 #define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
     const int n_pairs = n_seqs * kv.n_kv;
     if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster) {
@@ -1458,9 +1502,9 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     if (n_splits == 1 && n_pages > 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && second_pass))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
-                                                stream, fused)
+                                                stream, fused, lengths_differ)
             : launch_decode_stream<D, 3, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
-                                                stream, fused);
+                                                stream, fused, lengths_differ);
         if (taken != kNotTaken) return taken;
     }
     const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
@@ -1555,6 +1599,7 @@ THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_
 // Which unsplit single-token steps the streaming kernel takes: 0: none (one block per pair);
 // 1 (default): those with more (sequence, kv head) pairs than it has resident blocks; 2: all.
 // stages: its tile buffers, 3 or 6.
+THN_API void thn_set_decode_stream_order(int by_length) { g_decode_stream_by_length = by_length ? 1 : 0; }
 THN_API void thn_set_decode_stream(int mode, int stages) {
     g_decode_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode;
     g_decode_stream_stages = stages >= 6 ? 6 : 3;
@@ -1562,14 +1607,16 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
 // n_pages: pages of the cache entry (0 if unknown: the kernels that need a map of it are left out).
+// lengths_differ: 0 if the caller knows the sequences to be about equally long (a kernel may then
+// skip what it would do to balance them); the result does not depend on it.
 // counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the
 // last block of each (sequence, kv head) combines the splits itself; null: a second kernel
 // combines them.
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window, float* scratch, int* counters, long long n_pages, int* err,
-                                      cudaStream_t stream) {
+                                      int window, float* scratch, int* counters, long long n_pages, int lengths_differ,
+                                      int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
                   n_splits);
@@ -1583,9 +1630,9 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
     if (head_dim == 64)
         return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
-                                 counters, err, stream, FusedInput{}, n_pages);
+                                 counters, err, stream, FusedInput{}, n_pages, lengths_differ);
     return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
-                              counters, err, stream, FusedInput{}, n_pages);
+                              counters, err, stream, FusedInput{}, n_pages, lengths_differ);
 }
 
 // The same with the q/k norm, the rotation and the cache write of the step's token inside the
@@ -1598,8 +1645,8 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                                             int table_len, int write_cache, const int* row_slot, const int* row_pos,
                                             void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                             int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                            int window, float* scratch, int* counters, long long n_pages, int* err,
-                                            cudaStream_t stream) {
+                                            int window, float* scratch, int* counters, long long n_pages,
+                                            int lengths_differ, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode_fused: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode_fused: at most 32 splits with counters, got %d",
                   n_splits);
@@ -1617,9 +1664,9 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                      write_cache};
     if (head_dim == 64)
         return launch_decode<64, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                       window, counters, err, stream, fused, n_pages);
+                                       window, counters, err, stream, fused, n_pages, lengths_differ);
     return launch_decode<128, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                    window, counters, err, stream, fused, n_pages);
+                                    window, counters, err, stream, fused, n_pages, lengths_differ);
 }
 
 // ------------------------------------------------------------------ no device allocation
@@ -1680,5 +1727,6 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, err, stream);
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, /*lengths_differ=*/1, err,
+                                     stream);
 }

@@ -58,7 +58,7 @@ class DeviceBackend:
         self.out_tokens = torch.zeros(n, dtype=torch.int32, device=dev)
         self.row_slot = torch.zeros(n, dtype=torch.int32, device=dev)
         self.row_pos = torch.zeros(n, dtype=torch.int32, device=dev)
-        self.graphs: Dict[Tuple[int, int], torch.cuda.CUDAGraph] = {}     # (batch, context class)
+        self.graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}     # (batch, context class, lengths differ)
         self._composition: Optional[Tuple[int, ...]] = None
         ring = max(2, int(ring))
         self._ring = [(torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
@@ -66,7 +66,7 @@ class DeviceBackend:
         self._ring_busy = [False] * ring          # sent and not fetched yet
         self._stage = [torch.zeros(max(n, 1), dtype=torch.int32, pin_memory=True) for _ in range(ring)]
         self._ring_next = 0
-        self.graph_logits: Dict[Tuple[int, int], torch.Tensor] = {}    # the captured programs' logits
+        self.graph_logits: Dict[Tuple[int, int, bool], torch.Tensor] = {}    # the captured programs' logits
         # One slot with one page stays reserved: decode graphs are warmed up on it.
         (self._scratch_slot,) = cache.open(1)
         cache.prepare([self._scratch_slot], [1])
@@ -125,7 +125,7 @@ class DeviceBackend:
         self.chooser.choose(logits, slots_dev, out)
         return self._send(out, len(slots))
 
-    def _decode_program(self, batch: int, max_context: int) -> torch.Tensor:
+    def _decode_program(self, batch: int, max_context: int, lengths_differ: Optional[bool] = None) -> torch.Tensor:
         """One token for each of the first ``batch`` slots of ``slots_buf``: the step function's
         device side (``StepRunner.run_rows``) between a gather of each sequence's last token
         and the token choice.  Everything it reads and writes is per-sequence state or a
@@ -134,7 +134,8 @@ class DeviceBackend:
         slots = self.slots_buf[:batch]
         tokens = ops.gather_i32(self.last_token, slots, out=self.tokens_in[:batch])
         logits = self.runner.run_rows(tokens, self.cu_buf[:batch + 1], slots, batch, 1, max_context, None,
-                                      row_out=(self.row_slot[:batch], self.row_pos[:batch]))
+                                      row_out=(self.row_slot[:batch], self.row_pos[:batch]),
+                                      lengths_differ=lengths_differ)
         self.chooser.choose(logits, slots, self.out_tokens[:batch])
         return logits
 
@@ -147,7 +148,7 @@ class DeviceBackend:
         self.slots_buf[:len(slots)].copy_(stage[:len(slots)], non_blocking=True)
         self._composition = key
 
-    def _capture(self, batch: int, context_class: int, max_context: int) -> None:
+    def _capture(self, batch: int, context_class: int, max_context: int, differ: bool) -> None:
         """Warm the program up on the scratch slot (it advances nothing that lives), then
         record it."""
         scratch = torch.full((batch,), self._scratch_slot, dtype=torch.int32, device=self.device)
@@ -158,28 +159,29 @@ class DeviceBackend:
         with torch.cuda.stream(side):
             for _ in range(2):
                 self.cache.seq_lens[self._scratch_slot] = 0
-                self._decode_program(batch, max_context)
+                self._decode_program(batch, max_context, differ)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self.graph_logits[(batch, context_class)] = self._decode_program(batch, max_context)
+            self.graph_logits[(batch, context_class, differ)] = self._decode_program(batch, max_context, differ)
         self.cache.seq_lens[self._scratch_slot] = 0
         torch.cuda.synchronize()
-        self.graphs[(batch, context_class)] = graph
+        self.graphs[(batch, context_class, differ)] = graph
 
     def launch_decode(self, slots: Sequence[int]) -> _Handle:
         batch = len(slots)
-        longest = max(self.cache.length(slot) for slot in slots) + 1
-        context_class, max_context = ops.context_class(longest)
-        if self.use_graphs and (batch, context_class) not in self.graphs:
-            self._capture(batch, context_class, max_context)
+        lengths = [self.cache.length(slot) + 1 for slot in slots]
+        context_class, max_context = ops.context_class(max(lengths))
+        differ = ops.lengths_differ(lengths)
+        if self.use_graphs and (batch, context_class, differ) not in self.graphs:
+            self._capture(batch, context_class, max_context, differ)
         self.cache.prepare(list(slots), [1] * batch)          # a block-table update only at page boundaries
         self._set_composition(slots)
         if self.use_graphs:
-            self.graphs[(batch, context_class)].replay()
+            self.graphs[(batch, context_class, differ)].replay()
         else:
-            self._decode_program(batch, max_context)
+            self._decode_program(batch, max_context, differ)
         self.cache.commit(list(slots), [1] * batch)
         return self._send(self.out_tokens, batch)
 

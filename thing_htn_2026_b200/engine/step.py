@@ -63,14 +63,15 @@ class StepRunner:
     def run_rows(self, tokens: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, n_rows: int,
                  max_q_len: int, max_context: Optional[int], want_rows: Optional[torch.Tensor],
                  inputs: Optional[Dict[str, torch.Tensor]] = None,
-                 row_out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Optional[torch.Tensor]:
+                 row_out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                 lengths_differ: Optional[bool] = None) -> Optional[torch.Tensor]:
         """The device side of a step, and the only forward pass there is: rows and positions
         from the sequences' lengths, the scheduled layers from the cache, final norm and head
         at ``want_rows`` (int32 row indices; None: every row; empty: none, returns None),
         lengths advanced.  Every argument lives on the device and nothing here synchronises,
         so the same call is recorded into the generation loop's decode graphs."""
         rows = ops.step_rows(cu_seqlens, slots, self.cache.seq_lens, n_rows, max_q_len, out=row_out,
-                             max_context=max_context)
+                             max_context=max_context, lengths_differ=lengths_differ)
         ctx = StepContext(rows=rows, cache=self.cache, err=self.err, inputs=inputs or {})
         h, d = self.model.hidden(tokens, ctx)
         logits = None
@@ -114,7 +115,8 @@ class StepRunner:
         inputs = dict(zip(names, views[4:]))
 
         longest = max(h + c for h, c in zip(held, counts))
-        logits = self.run_rows(tokens, cu_dev, slots_dev, n_rows, max(counts), longest, want_dev, inputs)
+        logits = self.run_rows(tokens, cu_dev, slots_dev, n_rows, max(counts), longest, want_dev, inputs,
+                               lengths_differ=ops.lengths_differ([h + c for h, c in zip(held, counts)]))
         if logits is None:
             logits = torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
         self.cache.commit(slots, counts)

@@ -52,8 +52,8 @@ _SIGNATURES = {
                                c_int, c_int, c_int, c_void_p, c_void_p],
     "thn_attention_decode_fused_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
-                                        c_void_p],
+                                        c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                        c_void_p, c_void_p],
     "thn_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
     "thn_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -65,8 +65,8 @@ _SIGNATURES = {
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p,
-                                  c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                  c_void_p, c_void_p],
     "thn_attention_decode_blocks_per_sm": [c_int],
     "thn_attention_decode_cluster_splits": [],
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
@@ -100,6 +100,9 @@ def lib():
         loaded.thn_set_decode_cluster.argtypes = [c_int]
         loaded.thn_set_decode_cluster.restype = None
         loaded.thn_set_decode_cluster(0 if os.environ.get("THN_DECODE_CLUSTER", "1").strip() in ("0", "false", "off") else 1)
+        loaded.thn_set_decode_stream_order.argtypes = [c_int]
+        loaded.thn_set_decode_stream_order.restype = None
+        loaded.thn_set_decode_stream_order(int(os.environ.get("THN_DECODE_STREAM_BY_LENGTH", 1)))
         loaded.thn_set_decode_stream.argtypes = [c_int, c_int]
         loaded.thn_set_decode_stream.restype = None
         loaded.thn_set_decode_stream(int(os.environ.get("THN_DECODE_STREAM", 1)),
@@ -183,6 +186,9 @@ class StepRows:
     # Kernels may divide their work by it, which changes a result by rounding at most.  A step
     # captured as a graph is replayed only while its bound holds (see context_class).
     max_context: Optional[int] = None
+    # Host knowledge: False if the sequences of the step hold about the same number of keys (see
+    # lengths_differ); None: unknown.  Like max_context a hint that changes no result.
+    lengths_differ: Optional[bool] = None
 
 
 LONG_CONTEXT = 8192     # keys; a single-token step of few long sequences divides each key range further
@@ -196,9 +202,16 @@ def context_class(longest: int) -> Tuple[int, int]:
     return k, (LONG_CONTEXT << k) - 1
 
 
+def lengths_differ(lengths) -> bool:
+    """Whether the shortest of the sequences is more than a quarter shorter than the longest:
+    the class of a step, beside ``context_class``, by which a captured graph is chosen."""
+    longest = max(lengths)
+    return (longest - min(lengths)) * 4 > longest
+
+
 def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Tensor, n_rows: int,
               max_q_len: int, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-              max_context: Optional[int] = None) -> StepRows:
+              max_context: Optional[int] = None, lengths_differ: Optional[bool] = None) -> StepRows:
     _need(cu_seqlens, "step_rows cu_seqlens", torch.int32)
     _need(slots, "step_rows slots", torch.int32)
     _need(seq_lens, "step_rows seq_lens", torch.int32)
@@ -210,7 +223,8 @@ def step_rows(cu_seqlens: torch.Tensor, slots: torch.Tensor, seq_lens: torch.Ten
         row_slot, row_pos = out
     _call("thn_step_rows", _ptr(row_slot), _ptr(row_pos), _ptr(cu_seqlens), _ptr(slots), _ptr(seq_lens), n_seqs,
           _stream())
-    return StepRows(row_slot, row_pos, slots, cu_seqlens, n_rows, n_seqs, max_q_len, max_context=max_context)
+    return StepRows(row_slot, row_pos, slots, cu_seqlens, n_rows, n_seqs, max_q_len, max_context=max_context,
+                    lengths_differ=lengths_differ)
 
 
 def advance(seq_lens: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor) -> None:
@@ -611,7 +625,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
           n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
-          _ptr(err), _stream())
+          0 if rows.lengths_differ is False else 1, _ptr(err), _stream())
     return out
 
 
@@ -646,7 +660,8 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
           _code(q_gain, "qk gains"), float(eps), _ptr(rotary.cos), _ptr(rotary.sin), rotary.cos.shape[0],
           int(bool(write_cache)), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_seqs, n_q, n_splits, float(scale),
-          int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0], _ptr(err), _stream())
+          int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
+          0 if rows.lengths_differ is False else 1, _ptr(err), _stream())
     return out
 
 
