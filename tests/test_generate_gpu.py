@@ -182,7 +182,7 @@ def test_greedy_across_classes_of_context_length(tiny_models, monkeypatch):
     first class ending at 128 keys the longer sequence passes through three classes while it
     generates, the shorter one ends earlier, and every token still is the plain argmax."""
     from thing_htn_2026_b200 import ops
-    monkeypatch.setattr(ops, "LONG_CONTEXT", 128)
+    monkeypatch.setattr(ops, "CONTEXT_CLASS_BASE", 128)
     name = "d"
     prompts = [tiny.tokens(name, n, 800 + i) for i, n in enumerate([100, 30])]
     engine = engine_for(tiny_models[name], "bfloat16")

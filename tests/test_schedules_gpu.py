@@ -192,6 +192,36 @@ def test_streaming_decode_attention_gives_the_same_bits_every_time(fused):
     assert worst <= 2e-3, f"differs from the one-block-per-pair kernel by {worst:.3e}"
 
 
+def test_many_long_sequences_go_to_the_streaming_kernel_by_the_hosts_hint():
+    """16 sequences on 8 kv heads are fewer pairs than the GPU holds blocks, so by their number
+    alone they would meet in clusters; told that they may hold a thousand keys and more, the
+    launcher leaves the key ranges whole and streams them.  The result is the same either way."""
+    o = ops()
+    dtype, n_q, n_kv, D = torch.bfloat16, 32, 8, 128
+    lengths = [1500, 1100, 40, 2000] * 4
+    fix = kernels.PagedFixture(n_kv, D, lengths, dtype)
+    rows, cu = fix.rows(lengths)
+    kernels.write_kv(fix, rows, kernels.rand((cu[-1], n_kv, D), dtype, 90), kernels.rand((cu[-1], n_kv, D), dtype, 91), n_q)
+    fix.advance(rows, lengths)
+    fix.cache.seq_lens -= 1                                   # the step's token is the last one written
+    rows = o.step_rows(torch.arange(len(lengths) + 1, dtype=torch.int32, device=DEV),
+                       torch.tensor(fix.slots, dtype=torch.int32, device=DEV), fix.cache.seq_lens, len(lengths), 1)
+    q = kernels.rand((len(lengths), n_q * D), dtype, 92).to(DEV)
+    err = o.new_error_word(DEV)
+    unhinted = o.attention_decode_bf16(q, rows, fix.kv, n_q, D ** -0.5, None, err)
+    assert o.lib().thn_attention_decode_last_variant() % 10 == 1        # clusters
+    rows.max_context, rows.lengths_differ = max(lengths), True
+    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=rows.max_context) == 1
+    hinted = o.attention_decode_bf16(q, rows, fix.kv, n_q, D ** -0.5, None, err)
+    assert o.lib().thn_attention_decode_last_variant() == 32            # streaming
+    rows.max_context = 700                                                # short: clusters again
+    o.attention_decode_bf16(q, rows, fix.kv, n_q, D ** -0.5, None, err)
+    assert o.lib().thn_attention_decode_last_variant() % 10 == 1
+    assert int(err.item()) == 0
+    kernels.close(hinted, unhinted, dtype, "hinted against unhinted")
+    assert (hinted.float() - unhinted.float()).abs().max().item() <= 2e-3
+
+
 def test_decode_attention_few_pairs_meets_in_a_cluster():
     """The counterpart: few pairs, splits that meet in a cluster's shared memory."""
     lengths = [700, 64, 65, 1, 333, 128]

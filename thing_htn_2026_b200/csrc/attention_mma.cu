@@ -1435,7 +1435,8 @@ constexpr int kNotTaken = -1;      // launch_decode_stream leaves the step to th
 template <int D, int STAGES, bool FUSED>
 int launch_decode_stream(void* out, const void* q, const int* row_slot, const int* row_pos, PagedKV kv,
                          long long n_pages, int n_seqs, int n_q, float scale, int window, int* err, cudaStream_t stream,
-                         const FusedInput& fused, int lengths_differ) {
+                         const FusedInput& fused, int hints) {
+    const int lengths_differ = hints & 1;
     const int G = n_q / kv.n_kv;
     // Ranking costs each block about a microsecond at its start and gains 9 % on lengths spread
     // over 64 to 2,048 keys: it is done where the caller says that the lengths differ.
@@ -1468,7 +1469,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
     }
     // As many blocks as are resident at once, fewer if that spreads the pairs more evenly.
     const long long n_pairs = (long long)n_seqs * kv.n_kv, resident = (long long)sm_count() * per_sm_for[G];
-    if (n_pairs <= resident && g_decode_stream < 2) return kNotTaken;     // nothing to stream across
+    if (n_pairs <= resident && g_decode_stream < 2 && !(hints & 2)) return kNotTaken;     // nothing to stream across
     const long long rounds = (n_pairs + resident - 1) / resident;
     const int grid = (int)((n_pairs + rounds - 1) / rounds);
     g_last_decode_variant = STAGES * 10 + 2;
@@ -1484,7 +1485,7 @@ int launch_decode_stream(void* out, const void* q, const int* row_slot, const in
 template <int D, bool FUSED = false>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
                   PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
-                  cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0, int lengths_differ = 1) {
+                  cudaStream_t stream, FusedInput fused = FusedInput{}, long long n_pages = 0, int hints = 1) {
 #define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
     const int n_pairs = n_seqs * kv.n_kv;
     if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster) {
@@ -1498,13 +1499,16 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     // such blocks with two tile buffers each); below that, one block per pair was as fast or
     // faster: 2.74 / 2.93 / 3.09 against 2.77 / 3.04 / 3.14 ms per step at batch 32 / 40 / 48,
     // and 3.43 / 3.47 against 3.24 / 3.34 ms at batch 56 / 64 (Qwen3-4B sizes, 8 kv heads).
+    // The caller may know better (hint 2: long sequences, where streaming won from about 128
+    // pairs of 1,024 keys on: 4.38 against 4.76 ms per step at batch 24 with 4,096 keys).
     const bool second_pass = (long long)n_pairs > (long long)sm_count() * decode_blocks_per_sm<D, 2>();
-    if (n_splits == 1 && n_pages > 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && second_pass))) {
+    const bool asked_for = (hints & 2) != 0;
+    if (n_splits == 1 && n_pages > 0 && (g_decode_stream == 2 || (g_decode_stream == 1 && (second_pass || asked_for)))) {
         const int taken = g_decode_stream_stages >= 6
             ? launch_decode_stream<D, 6, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
-                                                stream, fused, lengths_differ)
+                                                stream, fused, hints)
             : launch_decode_stream<D, 3, FUSED>(out, q, row_slot, row_pos, kv, n_pages, n_seqs, n_q, scale, window, err,
-                                                stream, fused, lengths_differ);
+                                                stream, fused, hints);
         if (taken != kNotTaken) return taken;
     }
     const long long n_blocks = (long long)n_pairs * n_splits, sms = sm_count();
@@ -1599,6 +1603,8 @@ THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_
 // Which unsplit single-token steps the streaming kernel takes: 0: none (one block per pair);
 // 1 (default): those with more (sequence, kv head) pairs than it has resident blocks; 2: all.
 // stages: its tile buffers, 3 or 6.
+// 1 unless the streaming kernel has been switched off.
+THN_API int thn_attention_decode_streams() { return g_decode_stream != 0; }
 THN_API void thn_set_decode_stream_order(int by_length) { g_decode_stream_by_length = by_length ? 1 : 0; }
 THN_API void thn_set_decode_stream(int mode, int stages) {
     g_decode_stream = mode < 0 ? 0 : mode > 2 ? 2 : mode;
@@ -1607,15 +1613,16 @@ THN_API void thn_set_decode_stream(int mode, int stages) {
 
 // One token per sequence: row b is sequence b.  scratch may be null when n_splits == 1.
 // n_pages: pages of the cache entry (0 if unknown: the kernels that need a map of it are left out).
-// lengths_differ: 0 if the caller knows the sequences to be about equally long (a kernel may then
-// skip what it would do to balance them); the result does not depend on it.
+// hints: what the caller knows of the step, as bits; no result depends on them.  1: the sequences
+// differ in length (0: about equally long, and a kernel may skip what it would do to balance
+// them).  2: the sequences are long and many enough for the streaming kernel (see launch_decode).
 // counters: n_seqs * n_kv ints, zero before the first call and left zero, with which the
 // last block of each (sequence, kv head) combines the splits itself; null: a second kernel
 // combines them.
 THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_slot, const int* row_pos,
                                       const void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                       int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
-                                      int window, float* scratch, int* counters, long long n_pages, int lengths_differ,
+                                      int window, float* scratch, int* counters, long long n_pages, int hints,
                                       int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode: at most 32 splits with counters, got %d",
@@ -1630,9 +1637,9 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     float* part_ml = scratch ? scratch + (size_t)n_seqs * n_q * n_splits * head_dim : nullptr;
     if (head_dim == 64)
         return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
-                                 counters, err, stream, FusedInput{}, n_pages, lengths_differ);
+                                 counters, err, stream, FusedInput{}, n_pages, hints);
     return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
-                              counters, err, stream, FusedInput{}, n_pages, lengths_differ);
+                              counters, err, stream, FusedInput{}, n_pages, hints);
 }
 
 // The same with the q/k norm, the rotation and the cache write of the step's token inside the
@@ -1646,7 +1653,7 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                                             void* kv_base, const int* block_table, int bt_stride, int n_kv,
                                             int page_size, int head_dim, int n_seqs, int n_q, int n_splits, float scale,
                                             int window, float* scratch, int* counters, long long n_pages,
-                                            int lengths_differ, int* err, cudaStream_t stream) {
+                                            int hints, int* err, cudaStream_t stream) {
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode_fused: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode_fused: at most 32 splits with counters, got %d",
                   n_splits);
@@ -1664,9 +1671,9 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
                      write_cache};
     if (head_dim == 64)
         return launch_decode<64, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                       window, counters, err, stream, fused, n_pages, lengths_differ);
+                                       window, counters, err, stream, fused, n_pages, hints);
     return launch_decode<128, true>(out, part_o, part_ml, nullptr, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale,
-                                    window, counters, err, stream, fused, n_pages, lengths_differ);
+                                    window, counters, err, stream, fused, n_pages, hints);
 }
 
 // ------------------------------------------------------------------ no device allocation
@@ -1727,6 +1734,6 @@ THN_API int thn_attention_decode_bf16_no_alloc(void* out, const void* q, const i
         if (scratch == nullptr) return THN_BAD_ARGUMENT;
     }
     return thn_attention_decode_bf16(out, q, row_slot, row_pos, kv_base, block_table, bt_stride, n_kv, page_size,
-                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, /*lengths_differ=*/1, err,
+                                     head_dim, n_seqs, n_q, n_splits, scale, window, scratch, nullptr, /*n_pages=*/0, /*hints=*/1, err,
                                      stream);
 }

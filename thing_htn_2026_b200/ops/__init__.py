@@ -72,6 +72,7 @@ _SIGNATURES = {
     "thn_attention_decode_one_wave_splits": [c_int, c_int, c_int],
     "thn_attention_prefill_tile_rows": [],
     "thn_attention_decode_last_variant": [],
+    "thn_attention_decode_streams": [],
     "thn_attention_tcgen05_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_tcgen05_test_skip_loads": [c_int],
     "thn_attention_prefill_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
@@ -192,14 +193,16 @@ class StepRows:
 
 
 LONG_CONTEXT = 8192     # keys; a single-token step of few long sequences divides each key range further
+CONTEXT_CLASS_BASE = 1024   # keys; the first class of context length ends below it
+STREAM_MIN_CONTEXT = 1024   # keys from which many unsplit sequences go to the streaming decode attention
 
 
 def context_class(longest: int) -> Tuple[int, int]:
     """(class, bound) of a step whose longest sequence holds ``longest`` keys: class 0 below
-    LONG_CONTEXT, then one class per doubling.  Steps of one class make the same choices, so
-    one captured graph serves them; ``bound`` is the class's ``max_context``."""
-    k = (max(0, int(longest)) // LONG_CONTEXT).bit_length()
-    return k, (LONG_CONTEXT << k) - 1
+    CONTEXT_CLASS_BASE, then one class per doubling.  Steps of one class make the same choices,
+    so one captured graph serves them; ``bound`` is the class's ``max_context``."""
+    k = (max(0, int(longest)) // CONTEXT_CLASS_BASE).bit_length()
+    return k, (CONTEXT_CLASS_BASE << k) - 1
 
 
 def lengths_differ(lengths) -> bool:
@@ -594,6 +597,9 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bo
     if os.environ.get("THN_DECODE_SPLITS"):
         return int(os.environ["THN_DECODE_SPLITS"])
     pairs = max(1, n_seqs * n_kv)
+    if context is not None and STREAM_MIN_CONTEXT <= context and pairs * 20 >= 17 * _sm_count_of(device) \
+            and lib().thn_attention_decode_streams():
+        return 1           # unsplit: the streaming kernel's step (see decode_hints)
     one_wave = lib().thn_attention_decode_one_wave_splits(head_dim, int(fused), pairs)
     if context is not None and context >= LONG_CONTEXT:
         # Few long sequences: a block works through its tiles one after the other, and a cluster's
@@ -604,6 +610,21 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bo
         if wide >= 2 * max(1, one_wave):
             return wide
     return max(1, one_wave)
+
+
+def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
+    """What the host knows of a single-token step, as the kernels' ``hints`` bits: 1 unless the
+    sequences are known to be about equally long; 2 if the step is unsplit, its sequences may
+    hold STREAM_MIN_CONTEXT keys or more, and its (sequence, kv head) pairs are about as many
+    as SMs or more (measured on B200, Qwen3-4B sizes, ms per step with one block per pair or a
+    cluster per pair against the streaming kernel: batch 16 / 24 / 32 / 48 at 2,048 keys 3.03 /
+    3.51 / 3.87 / 4.90 against 2.98 / 3.36 / 3.78 / 4.64; at 4,096 keys 3.85 / 4.76 / 5.42 / 7.46
+    against 3.69 / 4.38 / 5.18 / 6.75; level at 1,024 keys; batch 12 and below: the cluster)."""
+    hints = 0 if rows.lengths_differ is False else 1
+    if n_splits == 1 and rows.max_context is not None and rows.max_context >= STREAM_MIN_CONTEXT \
+            and rows.n_rows * n_kv * 20 >= 17 * _sm_count_of(device):
+        hints |= 2
+    return hints
 
 
 def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int, scale: float,
@@ -625,7 +646,7 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _call("thn_attention_decode_bf16", _ptr(out), _ptr(q), _ptr(rows.row_slot), _ptr(rows.row_pos),
           _ptr(kv.storage), _ptr(kv.block_table), kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim,
           n_seqs, n_q, n_splits, float(scale), int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
-          0 if rows.lengths_differ is False else 1, _ptr(err), _stream())
+          decode_hints(rows, kv.n_kv, n_splits, q.device), _ptr(err), _stream())
     return out
 
 
@@ -661,7 +682,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
           int(bool(write_cache)), _ptr(rows.row_slot), _ptr(rows.row_pos), _ptr(kv.storage), _ptr(kv.block_table),
           kv.block_table.shape[1], kv.n_kv, kv.page_size, kv.head_dim, n_seqs, n_q, n_splits, float(scale),
           int(window or 0), _ptr(scratch), _ptr(counters), kv.storage.shape[0],
-          0 if rows.lengths_differ is False else 1, _ptr(err), _stream())
+          decode_hints(rows, kv.n_kv, n_splits, qkv.device), _ptr(err), _stream())
     return out
 
 
