@@ -210,8 +210,9 @@ def test_many_long_sequences_go_to_the_streaming_kernel_by_the_hosts_hint():
     err = o.new_error_word(DEV)
     unhinted = o.attention_decode_bf16(q, rows, fix.kv, n_q, D ** -0.5, None, err)
     assert o.lib().thn_attention_decode_last_variant() % 10 == 1        # clusters
-    rows.max_context, rows.lengths_differ = max(lengths), True
-    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=rows.max_context) == 1
+    rows.max_context, rows.lengths_differ = max(lengths), False       # (told so; the kernels believe the host)
+    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=rows.max_context, differ=False) == 1
+    assert o.decode_splits(len(lengths), n_kv, DEV, D, context=rows.max_context, differ=True) > 1   # too few to pair up
     hinted = o.attention_decode_bf16(q, rows, fix.kv, n_q, D ** -0.5, None, err)
     assert o.lib().thn_attention_decode_last_variant() == 32            # streaming
     rows.max_context = 700                                                # short: clusters again

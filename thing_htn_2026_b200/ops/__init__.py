@@ -588,7 +588,7 @@ DECODE_MAX_SPLITS = 32     # the splits of a key range are combined by the lanes
 
 
 def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bool = False,
-                  context: Optional[int] = None) -> int:
+                  context: Optional[int] = None, differ: Optional[bool] = None) -> int:
     """Splits of the key range per (sequence, kv head) of a single-token step: as many as fill
     the SMs once, the splits of a pair being the blocks of one thread-block cluster (at most
     eight, six unless the pairs are very few), all clusters resident at once.  It depends on the
@@ -597,9 +597,8 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bo
     if os.environ.get("THN_DECODE_SPLITS"):
         return int(os.environ["THN_DECODE_SPLITS"])
     pairs = max(1, n_seqs * n_kv)
-    if context is not None and STREAM_MIN_CONTEXT <= context and pairs * 20 >= 17 * _sm_count_of(device) \
-            and lib().thn_attention_decode_streams():
-        return 1           # unsplit: the streaming kernel's step (see decode_hints)
+    if long_sequences_stream(n_seqs, n_kv, context, differ, device):
+        return 1           # unsplit: the streaming kernel's step
     one_wave = lib().thn_attention_decode_one_wave_splits(head_dim, int(fused), pairs)
     if context is not None and context >= LONG_CONTEXT:
         # Few long sequences: a block works through its tiles one after the other, and a cluster's
@@ -612,17 +611,31 @@ def decode_splits(n_seqs: int, n_kv: int, device, head_dim: int = 128, fused: bo
     return max(1, one_wave)
 
 
+def long_sequences_stream(n_seqs: int, n_kv: int, context: Optional[int], differ: Optional[bool], device) -> bool:
+    """Whether a single-token step is one for the streaming decode attention by what the host
+    knows: sequences that may hold STREAM_MIN_CONTEXT keys or more, about as many (sequence, kv
+    head) pairs as SMs or more, and, if the lengths differ, at least two pairs per resident
+    block, so that long and short ones can be paired (with one pair per block the longest
+    sequence alone would set the time: 4.18 against 4.08 ms per step at batch 16 with 117 to
+    2,026 keys, Qwen3-8B sizes).  Measured on B200, Qwen3-4B sizes, equal lengths, ms per step
+    with one block or one cluster per pair against the streaming kernel: batch 16 / 24 / 32 / 48
+    at 2,048 keys 3.03 / 3.51 / 3.87 / 4.90 against 2.98 / 3.36 / 3.78 / 4.64; at 4,096 keys
+    3.85 / 4.76 / 5.42 / 7.46 against 3.69 / 4.38 / 5.18 / 6.75; level at 1,024 keys; batch 12
+    and below: the cluster."""
+    if context is None or context < STREAM_MIN_CONTEXT or not lib().thn_attention_decode_streams():
+        return False
+    pairs, sms = n_seqs * n_kv, _sm_count_of(device)
+    if differ is not False:
+        return pairs >= 4 * sms          # two blocks per SM, two pairs per block
+    return pairs * 20 >= 17 * sms
+
+
 def decode_hints(rows: StepRows, n_kv: int, n_splits: int, device) -> int:
     """What the host knows of a single-token step, as the kernels' ``hints`` bits: 1 unless the
-    sequences are known to be about equally long; 2 if the step is unsplit, its sequences may
-    hold STREAM_MIN_CONTEXT keys or more, and its (sequence, kv head) pairs are about as many
-    as SMs or more (measured on B200, Qwen3-4B sizes, ms per step with one block per pair or a
-    cluster per pair against the streaming kernel: batch 16 / 24 / 32 / 48 at 2,048 keys 3.03 /
-    3.51 / 3.87 / 4.90 against 2.98 / 3.36 / 3.78 / 4.64; at 4,096 keys 3.85 / 4.76 / 5.42 / 7.46
-    against 3.69 / 4.38 / 5.18 / 6.75; level at 1,024 keys; batch 12 and below: the cluster)."""
+    sequences are known to be about equally long; 2 if the step is unsplit and
+    :func:`long_sequences_stream` says so."""
     hints = 0 if rows.lengths_differ is False else 1
-    if n_splits == 1 and rows.max_context is not None and rows.max_context >= STREAM_MIN_CONTEXT \
-            and rows.n_rows * n_kv * 20 >= 17 * _sm_count_of(device):
+    if n_splits == 1 and long_sequences_stream(rows.n_rows, n_kv, rows.max_context, rows.lengths_differ, device):
         hints |= 2
     return hints
 
@@ -635,7 +648,8 @@ def attention_decode_bf16(q: torch.Tensor, rows: StepRows, kv: KVView, n_q: int,
     _need(q, "attention q", torch.bfloat16)
     n_seqs = rows.n_rows
     if n_splits is None:
-        n_splits = decode_splits(n_seqs, kv.n_kv, q.device, kv.head_dim, context=rows.max_context)
+        n_splits = decode_splits(n_seqs, kv.n_kv, q.device, kv.head_dim, context=rows.max_context,
+                                 differ=rows.lengths_differ)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     if need and scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
@@ -672,7 +686,8 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     width = (n_q + 2 * kv.n_kv) * kv.head_dim
     if tuple(qkv.shape) != (n_seqs, width):
         raise KernelError(f"qkv_attention: qkv is {tuple(qkv.shape)}, expected {(n_seqs, width)}")
-    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim, fused=True, context=rows.max_context)
+    n_splits = decode_splits(n_seqs, kv.n_kv, qkv.device, kv.head_dim, fused=True, context=rows.max_context,
+                             differ=rows.lengths_differ)
     need = lib().thn_attention_decode_scratch_floats(n_seqs, n_q, n_splits, kv.head_dim)
     scratch = torch.empty(need, dtype=torch.float32, device=qkv.device) if need else None
     counters = _counter_buffer(n_seqs * kv.n_kv, qkv.device) if n_splits > 1 else None
