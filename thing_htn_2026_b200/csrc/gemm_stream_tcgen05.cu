@@ -90,6 +90,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         }
     }
 }
+// The same without parking: for the two single threads that feed the ring and issue the
+// products, whose every wait stands between HBM and the tensor core.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    unsigned long long start = 0;
+    for (int spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 63) == 63) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > kWaitLimitNs) return false;
+        }
+    }
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -240,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
                     for (int i = 0; i < early; ++i) load_x(i, early_chunk[i]);
                     waited = true;
                 }
-                if (!mbar_wait(empty + s, ((it / S::kStages) & 1) ^ 1)) {
+                if (!mbar_wait_spin(empty + s, ((it / S::kStages) & 1) ^ 1)) {
                     if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                     *give_up = 1;
                     ok = false;
@@ -268,7 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_kernel(
             const uint32_t tmem_d = tmem_base + buf * S::kAccCols;
             for (int c = seg.c0; c < seg.c1 && ok; ++c, ++it) {
                 const int s = it % S::kStages;
-                ok = mbar_wait(full + s, (it / S::kStages) & 1);
+                ok = mbar_wait_spin(full + s, (it / S::kStages) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t w_addr = smem_addr(tiles + (size_t)s * S::kStageBytes);
@@ -482,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
         int it = early;
         for (int c = c0 + early; c < c1 && !*give_up; ++c, ++it) {
             const int s = it % kStages;
-            if (!mbar_wait(empty + s, ((it / kStages) & 1) ^ 1)) {
+            if (!mbar_wait_spin(empty + s, ((it / kStages) & 1) ^ 1)) {
                 if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
                 *give_up = 1;
                 break;
@@ -496,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_stream_cluster_kernel(
         int it = 0;
         for (int c = c0; c < c1 && ok && !*give_up; ++c, ++it) {
             const int s = it % kStages;
-            ok = mbar_wait(full + s, (it / kStages) & 1);
+            ok = mbar_wait_spin(full + s, (it / kStages) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t w_addr = smem_addr(tiles + (size_t)s * S::kStageBytes);
