@@ -40,7 +40,7 @@ constexpr uint32_t kQBytes = kRows * D * 2;       // 32 KB: two [128 x 64] swizz
 constexpr uint32_t kKBytes = kKeys * D * 2;       // 16 KB: two [64 x 64] blocks
 constexpr uint32_t kVBytes = kKeys * D * 2;       // 16 KB: two [64 keys x 64 d] blocks
 constexpr uint32_t kStageBytes = kKBytes + kVBytes;
-constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + 128;   // two blocks fit one SM
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + 256;   // two blocks fit one SM
 constexpr unsigned long long kWaitLimitNs = 20ull * 1000 * 1000;   // a wait gives up after 20 ms
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -221,9 +221,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
     uint64_t* v_full = k_empty + kStages;        // [kStages] the same for the V page
     uint64_t* v_empty = v_full + kStages;        // [kStages] (free after O += P V)
     uint64_t* s_full = v_empty + kStages;        // [2] S = Q K^T of a tile is in tensor memory (two buffers)
-    uint64_t* p_ready = s_full + 2;              // P of this tile is in tensor memory (4 arrivals)
-    uint64_t* o_full = p_ready + 1;              // O += P V of this tile is done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    uint64_t* p_ready = s_full + 2;              // [2] P of a tile is in its S buffer (4 arrivals).  One per buffer: a
+                                                 // warp that is a tile ahead of the others arrives on the other one
+    uint64_t* o_full = p_ready + 2;              // O += P V of this tile is done
+    uint64_t* o_done = o_full + 1;               // the block's last O += P V is done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     volatile int* give_up = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -247,7 +249,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
         mbar_init(s_full, 1);
         mbar_init(s_full + 1, 1);
         mbar_init(p_ready, 4);
+        mbar_init(p_ready + 1, 4);
         mbar_init(o_full, 1);
+        mbar_init(o_done, 1);
         *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 ok = qk(it + 1);
                 if (!ok) break;
             }
-            ok = mbar_wait_spin(p_ready, it & 1);      // P is in tensor memory; O has been rescaled
+            ok = mbar_wait_spin(p_ready + (it & 1), (it >> 1) & 1);      // P is in tensor memory; O has been rescaled
             if (!ok) break;
             const int s = it % kStages;
             ok = mbar_wait_spin(v_full + s, (it / kStages) & 1);
@@ -340,6 +344,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             }
             umma_commit(v_empty + s);             // the V page is free when these products are done
             umma_commit(o_full);
+            if (it + 1 == n_it) umma_commit(o_done);
         }
         if (!ok) {
             if (err) atomicOr(err, THN_ERR_WAIT_TIMEOUT);
@@ -410,7 +415,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
                 }
             }
             // O is rescaled only when some row of the warp moved its reference point; then the
-            // previous O += P V must be complete first.  tcgen05.ld/st are warp-wide, so the whole
+            // previous O += P V must be complete first (S of this tile says that the one before
+            // that is, so the parity is unambiguous).  tcgen05.ld/st are warp-wide, so the whole
             // warp goes if any of its rows must.
             if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 ok = __all_sync(0xffffffffu, mbar_wait(o_full, (it - 1) & 1));
@@ -441,10 +447,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tcgen05_kernel(
             run_sum = run_sum * corr + sum;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready);
+            if (lane == 0) mbar_arrive(p_ready + (it & 1));
         }
         if (ok && !*give_up && it > 0) {             // (ok is the same in every lane: see the waits above)
-            ok = __all_sync(0xffffffffu, mbar_wait(o_full, (it - 1) & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait(o_done, 0));
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float inv = 1.0f / run_sum;
