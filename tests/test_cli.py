@@ -41,7 +41,7 @@ def test_prompt_lens_and_named_configurations(tmp_path, capsys):
         named_config_json("qwen3-1t")
     # random-model runs without a device: a folder from a named configuration
     out = str(tmp_path / "m")
-    assert cli.main(["random-model", "--random-config", "tiny-b", "--seed", "1", "--out", out, "--dtype", "float32"]) == 0
+    assert cli.main(["random-model", "--random-config", "tiny-b", "--seed", "1", "--out", out, "--dtype", "fp32"]) == 0   # = float32
     assert sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
     assert json.load(open(os.path.join(out, "config.json")))["num_key_value_heads"] == 1
     with pytest.raises(SystemExit):

@@ -161,9 +161,15 @@ def _model_options(p) -> None:
                    help="random weights of a named configuration: " + ", ".join(named_configs()))
     p.add_argument("--layers", type=int, default=0, help="with --random-config: fewer layers (0 = all)")
     p.add_argument("--device", default="cuda:0")
-    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--dtype", default="bfloat16", type=_dtype_name, choices=["bfloat16", "float32"],
+                   help="bfloat16 (bf16) or float32 (fp32)")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
+
+
+def _dtype_name(text: str) -> str:
+    """``bf16`` and ``fp32`` are accepted for ``bfloat16`` and ``float32``."""
+    return {"bf16": "bfloat16", "fp32": "float32"}.get(text.lower(), text.lower())
 
 
 def main(argv=None) -> int:
@@ -198,7 +204,7 @@ def main(argv=None) -> int:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--out", required=True)
     r.add_argument("--device", default="cpu", help="where the values are drawn (cuda:0 draws a large model in seconds)")
-    r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--dtype", default="bfloat16", type=_dtype_name, choices=["bfloat16", "float32"])
     r.add_argument("--matrix-std", type=float, default=0.02)
     r.add_argument("--gain-std", type=float, default=0.02)
     r.set_defaults(run=_cmd_random_model)
