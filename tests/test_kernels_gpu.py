@@ -311,6 +311,37 @@ def test_attention_prefill_tensor_cores(n_q, n_kv, D, window):
     close(got, want, dtype, "prefill attention, continued prompts")
 
 
+@pytest.mark.parametrize("splits", ["", "1", "3", "8", "12"])
+@pytest.mark.parametrize("n_q,n_kv,D,window", [(4, 2, 32, None), (6, 3, 48, 70), (8, 2, 80, None), (16, 1, 96, None),
+                                               (5, 5, 112, 200), (32, 2, 96, 90)])
+def test_attention_tensor_cores_at_other_head_sizes(n_q, n_kv, D, window, splits):
+    """Head sizes in steps of 16 between 32 and 128 other than 64 and 128: the same prompt and
+    single-token kernels with two tile buffers, splits meeting in a cluster (3, 8) or through
+    scratch memory (12), against the plain implementation."""
+    dtype = torch.bfloat16
+    assert ops().lib().thn_attention_mma_supported(D, 64, n_q, n_kv) == 1
+    assert ops().lib().thn_attention_fused_supported(D, 64, n_q, n_kv) == 0
+    lengths = [700, 64, 65, 1, 333, 128]
+    got, want = attention_case("decode" + splits, dtype, n_q, n_kv, D, lengths, [1] * len(lengths), window)
+    close(got, want, dtype, f"decode attention, head size {D}, splits {splits or 'auto'}")
+    if splits == "":
+        got, want = attention_case("prefill", dtype, n_q, n_kv, D, [70, 5, 131, 64, 1, 257], [70, 5, 131, 64, 1, 257], window)
+        close(got, want, dtype, f"prefill attention, head size {D}, whole prompts")
+        got, want = attention_case("prefill", dtype, n_q, n_kv, D, [300, 90, 129], [170, 64, 1], window)
+        close(got, want, dtype, f"prefill attention, head size {D}, continued prompts")
+
+
+def test_attention_head_sizes_the_tensor_core_kernels_refuse():
+    o = ops()
+    for D in (16, 24, 40, 136, 144, 256):
+        assert o.lib().thn_attention_mma_supported(D, 64, 4, 2) == 0, D
+    for D in (32, 48, 64, 80, 96, 112, 128):
+        assert o.lib().thn_attention_mma_supported(D, 64, 4, 2) == 1, D
+        assert o.lib().thn_attention_fused_supported(D, 64, 4, 2) == (1 if D in (64, 128) else 0), D
+    assert o.lib().thn_attention_mma_supported(64, 64, 34, 2) == 0      # 17 query heads per kv head
+    assert o.lib().thn_attention_mma_supported(64, 32, 4, 2) == 0       # pages of 32 tokens
+
+
 @pytest.mark.parametrize("n_q,n_kv,window", [(2, 1, None), (8, 2, None), (6, 3, 70), (3, 1, 24), (5, 5, 200)])
 def test_attention_prefill_tcgen05(n_q, n_kv, window):
     """The tcgen05 prompt kernel: whole prompts (one row to several tiles) and continued ones."""

@@ -363,14 +363,15 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     int* __restrict__ err, FusedInput fused) {
     pdl_launch_dependents();
     pdl_wait();
+    static_assert(!FUSED || D % 64 == 0, "the fused prologue deals D / 64 values of each half of a head to a lane");
     constexpr int kPitch = D + 8, kStages = STAGES;
-    constexpr int E = D / 64, kHalf = D / 2;
+    constexpr int E = D >= 64 ? D / 64 : 1, kHalf = D / 2;
     // FUSED: the step's raw rows and the gains are requested first, so that they travel while
     // the block finds its pages (position -> page -> tile is a chain of dependent loads).
     __nv_bfloat16 raw_lo[E], raw_hi[E];                    // query head `warp` of the group (heads warp + 4, .. are read later)
     __nv_bfloat16 raw_k_lo[E], raw_k_hi[E], new_v_lo[E], new_v_hi[E];   // warp 0: the step's own key and value
     float qg_lo[E], qg_hi[E], kg_lo[E], kg_hi[E];
-    if (FUSED) {
+    if constexpr (FUSED) {
         const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5, d0 = lane_ * E;
         const int G_ = n_q / kv.n_kv;
         const __nv_bfloat16* row = fused.qkv + (size_t)blockIdx.x * (n_q + 2 * kv.n_kv) * D;
@@ -449,7 +450,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     };
     // FUSED: the row's angles are requested before the page of the first tile is looked up
     float angle_c[E], angle_s[E];
-    if (FUSED) {
+    if constexpr (FUSED) {
         const int at = pos < fused.table_len ? pos : 0;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
     int page_next = page_of(t_begin + kStages - 1);
 
     // the first tiles are on their way while the block prepares its queries
-    if (FUSED) {
+    if constexpr (FUSED) {
         if (pos >= fused.table_len) {
             if (threadIdx.x == 0 && err) atomicOr(err, THN_ERR_POSITION_RANGE);
             cp_async_wait<0>();
@@ -523,7 +524,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(
         issue(t + kStages - 1, stage == 0 ? kStages - 1 : stage - 1, page_now);     // into the buffer the last tile left
         cp_async_wait<kStages - 1>();
         __syncthreads();
-        if (FUSED && patches && t == t_last) {
+        if constexpr (FUSED) if (patches && t == t_last) {
             // the tile came from the cache without this step's token: put it in, here and there
             if (warp == 0) {
                 const int page = pages[t], in_page = pos % kTile, d0 = lane * E;
@@ -1528,12 +1529,51 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, const
     return thn_launch_status("attention_merge");
 }
 
+// Head sizes other than 64 and 128: the same single-token kernel with two tile buffers, the
+// query prepared by the separate kernel; the splits meet in a cluster where all clusters of
+// the step are resident, else through scratch memory.
+template <int D>
+int launch_decode_lite(void* out, float* part_o, float* part_ml, const void* q, const int* row_slot, const int* row_pos,
+                       PagedKV kv, int n_seqs, int n_q, int n_splits, float scale, int window, int* counters, int* err,
+                       cudaStream_t stream) {
+    const FusedInput fused{};
+#define THN_DECODE_ARGS out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream, fused
+    if (counters != nullptr && n_splits >= 2 && n_splits <= kMaxClusterSplits && g_decode_cluster &&
+        decode_clusters_resident<D, 2, false>(n_splits) >= n_seqs * kv.n_kv)
+        return launch_decode_with<D, 2, false, true>(THN_DECODE_ARGS);
+    const int status = launch_decode_with<D, 2, false, false>(THN_DECODE_ARGS);
+#undef THN_DECODE_ARGS
+    if (status != THN_OK || n_splits == 1 || counters != nullptr) return status;
+    thn_launch(attention_merge_kernel, n_seqs * n_q, D <= 64 ? 64 : 128, 0, stream, (__nv_bfloat16*)out, part_o, part_ml,
+               n_splits, D);
+    return thn_launch_status("attention_merge");
+}
+
+// CALL(D) for the head size at hand.  64 and 128 have every variant; the other multiples of 16
+// from 32 to 128 have the plain ones.
+#define THN_FOR_HEAD_DIM(head_dim, CALL) \
+    switch (head_dim) {                  \
+        case 32: CALL(32);               \
+        case 48: CALL(48);               \
+        case 64: CALL(64);               \
+        case 80: CALL(80);               \
+        case 96: CALL(96);               \
+        case 112: CALL(112);             \
+        default: CALL(128);              \
+    }
+
 }  // namespace
 
-// 1 if the tensor-core kernels take this shape (bfloat16 only), else 0.
+// 1 if the tensor-core kernels take this shape (bfloat16 only), else 0: head sizes in steps of
+// 16 from 32 to 128, pages of 64 tokens, at most 16 query heads per kv head.
 THN_API int thn_attention_mma_supported(int head_dim, int page_size, int n_q, int n_kv) {
-    return (head_dim == 64 || head_dim == 128) && page_size == kTile && n_kv > 0 && n_q % n_kv == 0 &&
-           n_q / n_kv <= 16;
+    return head_dim >= 32 && head_dim <= 128 && head_dim % 16 == 0 && page_size == kTile && n_kv > 0 &&
+           n_q % n_kv == 0 && n_q / n_kv <= 16;
+}
+
+// 1 if thn_attention_decode_fused_bf16 takes this shape: as above, with a head size of 64 or 128.
+THN_API int thn_attention_fused_supported(int head_dim, int page_size, int n_q, int n_kv) {
+    return (head_dim == 64 || head_dim == 128) && thn_attention_mma_supported(head_dim, page_size, n_q, n_kv);
 }
 
 // Tile buffers * 10 + (1: cluster, 2: streaming) of the most recent decode attention launch of this process.
@@ -1555,9 +1595,9 @@ THN_API int thn_attention_prefill_bf16(void* out, const void* q, const int* tile
                        head_dim, page_size, n_q, n_kv);
     if (n_tiles == 0) return THN_OK;
     PagedKV kv{kv_base, block_table, bt_stride, n_kv, page_size, head_dim};
-    if (head_dim == 64)
-        return launch_prefill<64>(out, q, tile_row0, tile_rows, n_tiles, row_slot, row_pos, kv, n_q, scale, window, err, stream);
-    return launch_prefill<128>(out, q, tile_row0, tile_rows, n_tiles, row_slot, row_pos, kv, n_q, scale, window, err, stream);
+#define CALL(D) return launch_prefill<D>(out, q, tile_row0, tile_rows, n_tiles, row_slot, row_pos, kv, n_q, scale, window, err, stream)
+    THN_FOR_HEAD_DIM(head_dim, CALL)
+#undef CALL
 }
 
 // Scratch floats needed by thn_attention_decode_bf16 for n_splits > 1: partial outputs
@@ -1570,7 +1610,9 @@ THN_API long long thn_attention_decode_scratch_floats(int n_seqs, int n_q, int n
 // Blocks of the decode kernel that one SM holds at a time (for choosing n_splits so that
 // the grid is one wave).
 THN_API int thn_attention_decode_blocks_per_sm(int head_dim) {
-    return head_dim == 64 ? decode_blocks_per_sm<64, 2>() : decode_blocks_per_sm<128, 2>();
+#define CALL(D) return decode_blocks_per_sm<D, 2>()
+    THN_FOR_HEAD_DIM(head_dim, CALL)
+#undef CALL
 }
 
 // 0: the splits of a sequence always meet in global memory; 1 (default): in a thread-block
@@ -1590,13 +1632,17 @@ THN_API int thn_attention_decode_cluster_splits() { return g_decode_cluster ? kM
 THN_API int thn_attention_decode_one_wave_splits(int head_dim, int fused, int n_pairs) {
     if (!g_decode_cluster || n_pairs <= 0) return 0;
     const int sms = sm_count();
-    const int per_sm = head_dim == 64 ? decode_blocks_per_sm<64, 2>() : decode_blocks_per_sm<128, 2>();
+    const int per_sm = thn_attention_decode_blocks_per_sm(head_dim);
     const int most = n_pairs * kMaxClusterSplits * 2 <= sms ? kMaxClusterSplits : 6;
-    for (int c = std::min(most, per_sm * sms / n_pairs); c >= 2; --c) {
-        const int fits = head_dim == 64 ? (fused ? decode_clusters_resident<64, 2, true>(c) : decode_clusters_resident<64, 2, false>(c))
-                                        : (fused ? decode_clusters_resident<128, 2, true>(c) : decode_clusters_resident<128, 2, false>(c));
-        if (fits >= n_pairs) return c;
-    }
+    auto resident = [&](int c) {
+        if (fused && head_dim == 64) return decode_clusters_resident<64, 2, true>(c);
+        if (fused && head_dim == 128) return decode_clusters_resident<128, 2, true>(c);
+#define CALL(D) return decode_clusters_resident<D, 2, false>(c)
+        THN_FOR_HEAD_DIM(head_dim, CALL)
+#undef CALL
+    };
+    for (int c = std::min(most, per_sm * sms / n_pairs); c >= 2; --c)
+        if (resident(c) >= n_pairs) return c;
     return 0;
 }
 
@@ -1638,8 +1684,12 @@ THN_API int thn_attention_decode_bf16(void* out, const void* q, const int* row_s
     if (head_dim == 64)
         return launch_decode<64>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
                                  counters, err, stream, FusedInput{}, n_pages, hints);
-    return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
-                              counters, err, stream, FusedInput{}, n_pages, hints);
+    if (head_dim == 128)
+        return launch_decode<128>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window,
+                                  counters, err, stream, FusedInput{}, n_pages, hints);
+#define CALL(D) return launch_decode_lite<D>(out, part_o, part_ml, q, row_slot, row_pos, kv, n_seqs, n_q, n_splits, scale, window, counters, err, stream)
+    THN_FOR_HEAD_DIM(head_dim, CALL)
+#undef CALL
 }
 
 // The same with the q/k norm, the rotation and the cache write of the step's token inside the
@@ -1657,8 +1707,8 @@ THN_API int thn_attention_decode_fused_bf16(void* out, const void* qkv, const vo
     THN_CHECK_ARG(n_seqs >= 0 && n_q > 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode_fused: bad sizes");
     THN_CHECK_ARG(counters == nullptr || n_splits <= 32, "attention_decode_fused: at most 32 splits with counters, got %d",
                   n_splits);
-    THN_UNSUPPORTED_IF(!thn_attention_mma_supported(head_dim, page_size, n_q, n_kv),
-                       "attention_decode_fused: head_dim %d, page %d, heads %d/%d not supported by the tensor-core kernel",
+    THN_UNSUPPORTED_IF(!thn_attention_fused_supported(head_dim, page_size, n_q, n_kv),
+                       "attention_decode_fused: head_dim %d, page %d, heads %d/%d not supported by the fused kernel",
                        head_dim, page_size, n_q, n_kv);
     THN_CHECK_ARG(qkv && q_gain && k_gain && cos_tab && sin_tab, "attention_decode_fused: gains and angles, please");
     THN_CHECK_ARG(w_dtype == THN_BF16 || w_dtype == THN_F32, "attention_decode_fused: unknown gain dtype %d", w_dtype);

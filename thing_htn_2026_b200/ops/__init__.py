@@ -62,6 +62,7 @@ _SIGNATURES = {
                           c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "thn_gather_i32": [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "thn_attention_mma_supported": [c_int, c_int, c_int, c_int],
+    "thn_attention_fused_supported": [c_int, c_int, c_int, c_int],
     "thn_attention_prefill_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "thn_attention_decode_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -678,7 +679,7 @@ def qkv_attention(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Opt
     fusable = (FUSE_DECODE_ATTENTION and rows.max_q_len == 1
                and qkv.dtype == torch.bfloat16 and q_gain is not None and k_gain is not None and rotary is not None
                and rotary.rotary_dim == kv.head_dim and kv.storage.dtype == torch.bfloat16
-               and lib().thn_attention_mma_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv))
+               and lib().thn_attention_fused_supported(kv.head_dim, kv.page_size, n_q, kv.n_kv))
     if not fusable:
         q = qk_norm_rope_cache(qkv, q_gain, k_gain, eps, rotary, rows, kv, n_q, write_cache, err)
         return attention(q, rows, kv, n_q, scale, window, err, tiles)
